@@ -1,5 +1,5 @@
 """One registry from an architecture's name (``architectures[0]`` of
-config.json) to its configuration class, whose ``model_spec`` describes the
+config.json, or its ``architecture`` string) to its configuration class, whose ``model_spec`` describes the
 model.  Reference: the ``ModelFamily`` seam (``src/family/mod.rs:11-82``) and
 ``ModelArch::from`` (``src/core/spec.rs:62-74``)."""
 from __future__ import annotations
@@ -23,8 +23,11 @@ def known_architectures() -> list:
 
 def architecture_name(data: dict) -> str:
     archs = data.get("architectures")
+    if archs is None and isinstance(data.get("architecture"), str):
+        return data["architecture"]
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("config.json: key 'architectures' must be a list that names the model class")
+        raise ConfigError("config.json: key 'architectures' must be a list that names the model class "
+                          "(or 'architecture' a string that does)")
     return archs[0]
 
 

@@ -452,3 +452,110 @@ AF_EXPORT int af_attn_decode_plain(void* out, int out_stride, const void* q, int
                         ring_rows, slopes));
   AF_CHECK_LAUNCH("af_attn_decode_plain");
 }
+
+// ---------------------------------------------------------------- norm + rope + cache write from a projection
+
+// Queries and keys that are normalised per head before they are rotated, and values that may be the
+// keys as projected.  The projection row of a token is float [q heads | k heads (| v heads)]; a warp per
+// (token, q or k head):
+//   n = x * rsqrt(mean(x^2) + eps) * weight   (weight of head_dim values shared by the heads; none: n = x)
+//   the first rot_dim elements of n rotated by position * frequency (32-bit), the rest kept
+// and written to the packed row [q | k | v] of the compute dtype; a k head also goes to its row of the
+// cache, and its value head (the raw x with `v_from_k`, else the projection's own v head) to the packed
+// row and the cache.
+template <typename T>
+__global__ void __launch_bounds__(128)
+qk_norm_rope_store_kernel(T* __restrict__ qkv, long long out_stride, const float* __restrict__ proj, long long ld,
+                          const float* __restrict__ q_weight, const float* __restrict__ k_weight, float eps,
+                          int v_from_k, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                          const int* __restrict__ slots, const int* __restrict__ len_after,
+                          const float* __restrict__ inv_freq, int n_tokens, int nq, int nkv, int hd, int rot_dim,
+                          int pairing, T* __restrict__ kcache, T* __restrict__ vcache,
+                          const int* __restrict__ page_table, int max_pages, int ring_rows) {
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31;
+  const long long wi = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (wi >= (long long)n_tokens * (nq + nkv)) return;
+  const int t = (int)(wi / (nq + nkv)), head = (int)(wi % (nq + nkv));
+  const bool is_k = head >= nq;
+  const int pos = positions[t];
+  // where a k head's row goes in the cache
+  T *kdst = nullptr, *vdst = nullptr;
+  if (kcache != nullptr && is_k) {
+    const int seq = seq_of_token[t];
+    const int slot = slots[seq];
+    if (slot >= 0 && !(ring_rows > 0 && pos + ring_rows < len_after[seq])) {
+      const int r = ring_rows > 0 ? pos % ring_rows : pos;
+      if (AF_INDEX_OK(pos >= 0 && r / AF_PAGE < max_pages, r)) {
+        const int page = page_table[(size_t)slot * max_pages + r / AF_PAGE];
+        if (AF_INDEX_OK(page >= 0, page)) {
+          const size_t at = (((size_t)page * nkv + (head - nq)) * AF_PAGE + r % AF_PAGE) * hd;
+          kdst = kcache + at;
+          vdst = vcache + at;
+        }
+      }
+    }
+  }
+  pdl_wait();
+  const float* x = proj + (size_t)t * ld + (size_t)head * hd;
+  const float* w = is_k ? k_weight : q_weight;
+  T* orow = qkv + (size_t)t * out_stride;
+  T* dst = orow + (size_t)head * hd;                        // q heads and k heads keep their places
+  float inv = 1.f;
+  if (w != nullptr) {
+    float ss = 0.f;
+    for (int i = lane; i < hd; i += 32) ss += x[i] * x[i];
+    ss = warp_sum(ss);
+    inv = rsqrtf(ss / (float)hd + eps);
+  }
+  const int half = rot_dim / 2;
+  for (int p = lane; p < half; p += 32) {
+    const int i0 = pairing == AF_PAIR_HALF ? p : 2 * p;
+    const int i1 = pairing == AF_PAIR_HALF ? p + half : 2 * p + 1;
+    const float a = w ? x[i0] * inv * w[i0] : x[i0], b = w ? x[i1] * inv * w[i1] : x[i1];
+    float s, c;
+    sincosf((float)pos * inv_freq[p], &s, &c);
+    const T ra = from_f32<T>(a * c - b * s), rb = from_f32<T>(b * c + a * s);
+    dst[i0] = ra, dst[i1] = rb;
+    if (kdst != nullptr) kdst[i0] = ra, kdst[i1] = rb;
+  }
+  for (int i = rot_dim + lane; i < hd; i += 32) {
+    const T v = from_f32<T>(w ? x[i] * inv * w[i] : x[i]);
+    dst[i] = v;
+    if (kdst != nullptr) kdst[i] = v;
+  }
+  if (is_k) {
+    const float* vx = v_from_k ? x : proj + (size_t)t * ld + (size_t)(head + nkv) * hd;
+    T* vrow = orow + (size_t)(head + nkv) * hd;
+    for (int i = lane; i < hd; i += 32) {
+      const T v = from_f32<T>(vx[i]);
+      vrow[i] = v;
+      if (vdst != nullptr) vdst[i] = v;
+    }
+  }
+}
+
+AF_EXPORT int af_qk_norm_rope_store(void* qkv, int dtype, long long out_stride, const float* proj, long long ld,
+                                    const float* q_weight, const float* k_weight, float eps, int v_from_k,
+                                    const int* positions, const int* seq_of_token, const int* slots,
+                                    const int* len_after, const float* inv_freq, int n_tokens, int nq, int nkv, int hd,
+                                    int rot_dim, int pairing, void* kcache, void* vcache, const int* page_table,
+                                    int max_pages, int ring_rows, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  AF_REQUIRE(n_tokens > 0 && nq > 0 && nkv > 0 && hd > 0, "af_qk_norm_rope_store: bad sizes");
+  AF_REQUIRE(rot_dim >= 0 && rot_dim <= hd && rot_dim % 2 == 0,
+             "af_qk_norm_rope_store: rotary dim %d must be even and <= head_dim %d", rot_dim, hd);
+  AF_REQUIRE(pairing == AF_PAIR_HALF || pairing == AF_PAIR_ADJACENT, "af_qk_norm_rope_store: pairing");
+  AF_REQUIRE(ring_rows % AF_PAGE == 0, "af_qk_norm_rope_store: ring rows %d not whole pages", ring_rows);
+  AF_REQUIRE((kcache == nullptr) == (vcache == nullptr), "af_qk_norm_rope_store: k and v cache");
+  AF_REQUIRE((q_weight == nullptr) == (k_weight == nullptr), "af_qk_norm_rope_store: both norm weights or none");
+  const long long warps = (long long)n_tokens * (nq + nkv);
+  const long long blocks = (warps + 3) / 4;
+  AF_REQUIRE(blocks < (1ll << 31), "af_qk_norm_rope_store: too many rows");
+  AF_DISPATCH_DTYPE(dtype, T,
+                    af_launch(qk_norm_rope_store_kernel<T>, dim3((unsigned)blocks), dim3(128), 0, stream, (T*)qkv,
+                              out_stride, proj, ld, q_weight, k_weight, eps, v_from_k, positions, seq_of_token, slots,
+                              len_after, inv_freq, n_tokens, nq, nkv, hd, rot_dim, pairing, (T*)kcache, (T*)vcache,
+                              page_table, max_pages, ring_rows));
+  AF_CHECK_LAUNCH("af_qk_norm_rope_store");
+}

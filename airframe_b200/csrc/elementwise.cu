@@ -472,3 +472,63 @@ AF_EXPORT int af_softcap(float* z, long long n, float cap, cudaStream_t stream) 
   af_launch(softcap_kernel, dim3((int)blocks), dim3(256), 0, stream, z, (size_t)n, cap);
   AF_CHECK_LAUNCH("af_softcap");
 }
+
+// ---------------------------------------------------------------- residual sum of weighted terms, then a norm
+
+// x += scale_a * a (+ scale_b * b); then, when y is given, y = norm(x) * (offset + w_next): the residual
+// sum of a pre-norm layer with the norm of the sublayer behind it.  Each term is a row of the compute
+// dtype or `n` float partial sums ([n, rows, hidden], added in index order).  One block per row; the new
+// row stays in shared memory between the sum and the norm.
+__device__ __forceinline__ float term_value(const void* p, int dtype, int n_parts, size_t part_stride, size_t at) {
+  if (dtype == AF_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[at]);
+  const float* f = static_cast<const float*>(p) + at;
+  float v = f[0];
+  for (int s = 1; s < n_parts; ++s) v += f[(size_t)s * part_stride];
+  return v;
+}
+
+template <typename TY>
+__global__ void __launch_bounds__(256)
+add_scaled_rmsnorm_kernel(float* __restrict__ x, const void* __restrict__ a, int a_dtype, int a_parts, float scale_a,
+                          const void* __restrict__ b, int b_dtype, int b_parts, float scale_b, size_t part_stride,
+                          TY* __restrict__ y, const float* __restrict__ w_next, int hidden, float eps, float offset) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float row[];
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  float* xr = x + (size_t)r * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const size_t at = (size_t)r * hidden + i;
+    float t = scale_a * term_value(a, a_dtype, a_parts, part_stride, at);
+    if (b != nullptr) t += scale_b * term_value(b, b_dtype, b_parts, part_stride, at);
+    const float v = xr[i] + t;
+    xr[i] = v;
+    row[i] = v;
+    ss += v * v;
+  }
+  if (y == nullptr) return;
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)hidden + eps);
+  TY* yr = y + (size_t)r * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) yr[i] = from_f32<TY>(row[i] * inv * (offset + w_next[i]));
+}
+
+AF_EXPORT int af_add_scaled_rmsnorm(float* x, const void* a, int a_dtype, int a_parts, float scale_a, const void* b,
+                                    int b_dtype, int b_parts, float scale_b, void* y, int y_dtype, const float* w_next,
+                                    int n_rows, int hidden, float eps, float offset, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  AF_REQUIRE(n_rows > 0 && hidden > 0 && a != nullptr && a_parts >= 1 && b_parts >= 1, "af_add_scaled_rmsnorm: bad sizes");
+  AF_REQUIRE((a_dtype == AF_F32 || (a_dtype == AF_BF16 && a_parts == 1)) &&
+             (b == nullptr || b_dtype == AF_F32 || (b_dtype == AF_BF16 && b_parts == 1)),
+             "af_add_scaled_rmsnorm: partial sums are float");
+  AF_REQUIRE((size_t)hidden * sizeof(float) <= 48 * 1024, "af_add_scaled_rmsnorm: rows of up to 12288 values");
+  AF_REQUIRE(y == nullptr || w_next != nullptr, "af_add_scaled_rmsnorm: a norm needs its weight");
+  const size_t part_stride = (size_t)n_rows * hidden;
+  AF_DISPATCH_DTYPE(y_dtype, TY,
+                    af_launch(add_scaled_rmsnorm_kernel<TY>, dim3(n_rows), dim3(256), (size_t)hidden * sizeof(float), stream,
+                              x, a, a_dtype, a_parts, scale_a, b, b_dtype, b_parts, scale_b, part_stride, (TY*)y, w_next,
+                              hidden, eps, offset));
+  AF_CHECK_LAUNCH("af_add_scaled_rmsnorm");
+}

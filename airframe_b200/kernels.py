@@ -238,6 +238,11 @@ def _no_frequencies(device):
     return _EMPTY_F32[key]
 
 
+def no_frequencies(device):
+    """An empty table of rotary frequencies (a rotation of no elements)."""
+    return _no_frequencies(device)
+
+
 def store_kv(qkv, batch, nq: int, nkv: int, hd: int, kv, parts=None) -> None:
     """A mixer's cache store: the k and v heads of the packed rows [q | k | v]
     go to each token's row of its cache page (``kv``: the layer's view of its
@@ -685,6 +690,175 @@ def attn_decode(out, q, kv, batch, nq, nkv, hd, scale, cap, window, slopes=None)
                       scale, cap, window, kv.ring_rows, slopes)
 
 
+# ---------------------------------------------------------------- mixers with a state of fixed size
+
+SCAN_MODES = {"decay": 0, "delta": 1}
+
+
+def _f32_rows(t, name):
+    """Pointer and token stride of float32 rows (a column section of a packed projection is fine)."""
+    if t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1:
+        raise KernelError(f"{name} must be float32 rows, got {t.dtype} {tuple(t.shape)} strides {t.stride()}")
+    return _ptr(t, name), c_longlong(t.stride(0))
+
+
+def delta_prep(out, proj, off_k: int, off_a: int, off_w1: int, a_bias, w0, w2, heads: int, dk: int,
+               decay_scale: float, key_eps: float) -> None:
+    """What enters the generalized delta rule besides r, k and v, from the packed float32 projection rows
+    ``proj`` (sections at the given column offsets): out [T, 3, heads * dk] float32 = the decay
+    exp(-decay_scale * sigmoid(w2 tanh(w1 section) + w0)), the unit key k / sqrt(sum k^2 + key_eps) per head,
+    and sigmoid(a section + a_bias) times the unit key."""
+    T = proj.shape[0]
+    n = heads * dk
+    rank = w2.shape[1]
+    if tuple(out.shape) != (T, 3, n) or out.dtype != torch.float32 or not out.is_contiguous():
+        raise KernelError(f"delta_prep: out must be contiguous float32 [{T}, 3, {n}]")
+    if tuple(w2.shape) != (n, rank) or not w2.is_contiguous() or a_bias.numel() != n or w0.numel() != n:
+        raise KernelError("delta_prep: w2 [heads * dk, rank], a_bias and w0 [heads * dk]")
+    if max(off_k, off_a) + n > proj.shape[1] or off_w1 + rank > proj.shape[1]:
+        raise KernelError("delta_prep: a section lies outside the projection row")
+    pp, ld = _f32_rows(proj, "proj")
+    _check(_lib().af_delta_prep(_ptr(out), pp, ld, c_int(off_k), c_int(off_a), c_int(off_w1),
+                                _ptr(a_bias, "a_bias", torch.float32), _ptr(w0, "w0", torch.float32),
+                                _ptr(w2, "w2", torch.float32), c_int(rank), c_int(T), c_int(heads), c_int(dk),
+                                c_float(decay_scale), c_float(key_eps), _stream()))
+
+
+def state_scan(mode: str, out, r, k, v, state, batch, heads: int, dk: int, dv: int, w=None, u=None, au=None,
+               decay=None, silu: bool = False) -> None:
+    """The recurrence of a matrix state per head over the step's tokens, sequence by sequence, from
+    the state that earlier steps left in ``state`` (float32 [slots, heads, dv, dk]; left updated):
+
+    ``decay``: S <- decay[h] S + k v^T, o = S^T r;
+    ``delta``: S <- diag(w) S - au (u^T S) + k v^T, o = S^T r (both terms read the old S).
+
+    r, k, w, u, au: float32 rows [T, heads * dk] (column sections allowed), v [T, heads * dv], out float32
+    [T, heads * dv].  ``silu``: r, k and v pass through x * sigmoid(x) as they are read."""
+    if mode not in SCAN_MODES:
+        raise KernelError(f"state_scan: unknown mode '{mode}'")
+    T = out.shape[0]
+    if state.dtype != torch.float32 or tuple(state.shape[1:]) != (heads, dv, dk) or not state.is_contiguous():
+        raise KernelError(f"state_scan: state must be contiguous float32 [slots, {heads}, {dv}, {dk}]")
+    for t, name, n in ((r, "r", dk), (k, "k", dk), (v, "v", dv), (out, "out", dv)):
+        if tuple(t.shape) != (T, heads * n):
+            raise KernelError(f"state_scan: {name} must be [{T}, {heads * n}], got {tuple(t.shape)}")
+    null = (ctypes.c_void_p(0), c_longlong(0))
+    if mode == "delta":
+        if w is None or u is None or au is None:
+            raise KernelError("state_scan: the delta rule needs w, u and au")
+        extra = [_f32_rows(t, n) for t, n in ((w, "w"), (u, "u"), (au, "au"))]
+        dec = ctypes.c_void_p(0)
+    else:
+        if decay is None or decay.numel() != heads:
+            raise KernelError("state_scan: one decay per head")
+        extra = [null, null, null]
+        dec = _ptr(decay, "decay", torch.float32)
+    rp, kp, vp, op = (_f32_rows(t, n) for t, n in ((r, "r"), (k, "k"), (v, "v"), (out, "out")))
+    _check(_lib().af_state_scan(c_int(SCAN_MODES[mode]), *rp, *kp, *vp, *extra[0], *extra[1], *extra[2], dec,
+                                _ptr(state, "state", torch.float32), *op,
+                                _ptr(batch.seq_starts, "seq_starts", torch.int32), _ptr(batch.slots, "slots", torch.int32),
+                                c_int(batch.n_seqs), c_int(heads), c_int(dk), c_int(dv), c_int(1 if silu else 0), _stream()))
+
+
+def gated_group_norm(y, o, w, gate, group: int, eps: float) -> None:
+    """y = o * rsqrt(mean over each group of ``group`` values of o^2 + eps) * w * sigmoid(gate);
+    o float32 [T, n] contiguous, gate float32 rows [T, n] (a column section is fine), w float32 [n]."""
+    T, n = o.shape
+    if o.dtype != torch.float32 or not o.is_contiguous() or tuple(y.shape) != (T, n) or not y.is_contiguous():
+        raise KernelError("gated_group_norm: o float32 and y, both contiguous [T, n]")
+    if w.numel() != n or tuple(gate.shape) != (T, n):
+        raise KernelError("gated_group_norm: weight [n] and gate [T, n]")
+    gp, gts = _f32_rows(gate, "gate")
+    _check(_lib().af_gated_group_norm(_ptr(y), c_int(dtype_code(y.dtype)), _ptr(o), _ptr(w, "w", torch.float32), gp, gts,
+                                      c_int(T), c_int(n), c_int(group), c_float(eps), _stream()))
+
+
+def gated_scan(y, proj, off_z: int, off_x: int, off_g: int, bz, bx, state, batch) -> None:
+    """A gated recurrence over a vector state, channel by channel: with the sections z, x, g of the packed
+    float32 projection rows, gate = sigmoid(z + bz), c = x + bx, candidate = c + 1/2 where c >= 0 and
+    sigmoid(c) below, S <- (1 - gate) S + gate * candidate, y = S * silu(g).  ``state`` float32
+    [slots, width] is read and left updated."""
+    T, width = y.shape
+    if not y.is_contiguous() or state.dtype != torch.float32 or tuple(state.shape[1:]) != (width,) \
+            or not state.is_contiguous():
+        raise KernelError(f"gated_scan: y contiguous [T, {width}], state contiguous float32 [slots, {width}]")
+    if max(off_z, off_x, off_g) + width > proj.shape[1] or bz.numel() != width or bx.numel() != width:
+        raise KernelError("gated_scan: a section lies outside the projection row, or a bias of another size")
+    pp, ld = _f32_rows(proj, "proj")
+    _check(_lib().af_gated_scan(_ptr(y), c_int(dtype_code(y.dtype)), pp, ld, c_int(off_z), c_int(off_x), c_int(off_g),
+                                _ptr(bz, "bz", torch.float32), _ptr(bx, "bx", torch.float32),
+                                _ptr(state, "state", torch.float32), _ptr(batch.seq_starts, "seq_starts", torch.int32),
+                                _ptr(batch.slots, "slots", torch.int32), c_int(batch.n_seqs), c_int(width), _stream()))
+
+
+def qk_norm_rope_store(qkv, proj, batch, nq: int, nkv: int, hd: int, inv_freq, rot_dim: int, pairing: str,
+                       q_weight=None, k_weight=None, eps: float = 0.0, v_from_k: bool = False, kv=None) -> None:
+    """From float32 projection rows [q heads | k heads (| v heads)]: q and k heads normalised per head
+    (x * rsqrt(mean x^2 + eps) * weight, the weight of ``hd`` values shared by the heads; no weights: as
+    they are), their first ``rot_dim`` elements rotated, into the packed rows ``qkv`` [q | k | v] of the
+    compute dtype; the value heads are the k heads as projected (``v_from_k``) or the projection's own.
+    With ``kv`` (the layer's view of its cache pages) k and v also go to each token's row of its page."""
+    T = proj.shape[0]
+    width_in = (nq + nkv) * hd if v_from_k else (nq + 2 * nkv) * hd
+    if proj.shape[1] < width_in or tuple(qkv.shape) != (T, (nq + 2 * nkv) * hd):
+        raise KernelError(f"qk_norm_rope_store: projection of {width_in} columns into rows of {(nq + 2 * nkv) * hd}")
+    if pairing not in PAIRINGS or inv_freq.numel() != rot_dim // 2:
+        raise KernelError("qk_norm_rope_store: pairing, or inv_freq does not hold rot_dim / 2 values")
+    for wgt in (q_weight, k_weight):
+        if wgt is not None and wgt.numel() != hd:
+            raise KernelError(f"qk_norm_rope_store: a norm weight of {hd} values")
+    kc = vc = pt = None
+    max_pages = ring = 0
+    if kv is not None:
+        kc, vc, pt, ring = kv.k, kv.v, kv.page_table, kv.ring_rows
+        if kc.dtype != qkv.dtype or tuple(kc.shape[1:]) != (nkv, PAGE, hd) or not kc.is_contiguous() \
+                or not vc.is_contiguous():
+            raise KernelError(f"qk_norm_rope_store: cache pages must be [pages, {nkv}, {PAGE}, {hd}] of the rows' dtype")
+        max_pages = pt.shape[1]
+    pp, ld = _f32_rows(proj, "proj")
+    _check(_lib().af_qk_norm_rope_store(
+        _ptr(qkv), c_int(dtype_code(qkv.dtype)), c_longlong(_rows(qkv, "qkv")), pp, ld,
+        _ptr(q_weight, "q_weight", torch.float32, allow_none=True),
+        _ptr(k_weight, "k_weight", torch.float32, allow_none=True), c_float(eps), c_int(1 if v_from_k else 0),
+        _ptr(batch.positions, "positions", torch.int32), _ptr(batch.seq_of_token, "seq_of_token", torch.int32),
+        _ptr(batch.slots, "slots", torch.int32), _ptr(batch.len_after, "len_after", torch.int32),
+        _ptr(inv_freq, "inv_freq", torch.float32), c_int(T), c_int(nq), c_int(nkv), c_int(hd), c_int(rot_dim),
+        c_int(PAIRINGS[pairing]), _ptr(kc, allow_none=True), _ptr(vc, allow_none=True),
+        _ptr(pt, "page_table", torch.int32, allow_none=True), c_int(max_pages), c_int(ring), _stream()))
+
+
+def add_scaled_rmsnorm(x, terms, y=None, w_next=None, eps: float = 0.0, offset: float = 0.0) -> None:
+    """x += sum of scale * term over ``terms`` (a list of (tensor, scale): a tensor [rows, H] of the
+    compute dtype, or float32 partial sums [n, rows, H], added in index order); then, when ``y`` is
+    given, y = norm(x) * (offset + w_next).  Two terms a kernel; the norm rides on the last."""
+    n, H = x.shape
+    if not x.is_contiguous() or (y is not None and not y.is_contiguous()):
+        raise KernelError("add_scaled_rmsnorm: tensors must be contiguous")
+    if not terms:
+        raise KernelError("add_scaled_rmsnorm: at least one term")
+
+    def arg(t):
+        parts = 1
+        if t.dim() == 3:
+            parts = t.shape[0]
+            if t.dtype != torch.float32:
+                raise KernelError("add_scaled_rmsnorm: partial sums are float32")
+        if tuple(t.shape[-2:]) != (n, H) or not t.is_contiguous():
+            raise KernelError(f"add_scaled_rmsnorm: a term of shape {tuple(t.shape)} for rows {(n, H)}")
+        return _ptr(t), c_int(dtype_code(t.dtype)), c_int(parts)
+
+    for i in range(0, len(terms), 2):
+        pair = terms[i:i + 2]
+        last = i + 2 >= len(terms)
+        a, sa = pair[0]
+        b, sb = pair[1] if len(pair) > 1 else (None, 0.0)
+        barg = arg(b) if b is not None else (ctypes.c_void_p(0), c_int(F32), c_int(1))
+        yy = y if last else None
+        _check(_lib().af_add_scaled_rmsnorm(
+            _ptr(x, "x", torch.float32), *arg(a), c_float(sa), *barg, c_float(sb), _ptr(yy, "y", allow_none=True),
+            c_int(dtype_code(yy.dtype) if yy is not None else F32),
+            _ptr(w_next, "w_next", torch.float32, allow_none=True) if yy is not None else ctypes.c_void_p(0),
+            c_int(n), c_int(H), c_float(eps), c_float(offset), _stream()))
 
 
 __all__ = [n for n in dir() if not n.startswith("_")]

@@ -7,6 +7,13 @@ v; query head h reads key/value head h // (heads / kv_heads).  Reference:
 ``:727-730``, online softmax ``:739-753``, head mapping ``:673,677``), the
 projections ``:499-530`` and ``:775-804``.  The reference fixes the scale at
 head_dim^-0.5 and has no window; both are parameters here.
+
+Two more options, for designs that have them: ``qk_norm`` (q and k heads are
+RMS-normed per head with a weight of head_dim values that all heads share,
+before any rotation) and values that are the keys as projected (no
+``v_weight``: v = W_k h, before norm and rotation).  With either, the
+projection goes into 32-bit rows and one kernel norms, rotates, packs
+[q | k | v] and writes the cache.
 """
 from __future__ import annotations
 
@@ -15,8 +22,9 @@ import torch
 from .. import kernels
 from ..config.base import ConfigError, PartSpec
 from ..weights.loader import WeightDecl
-from .base import KVNeed, Mixer, build_part, register_part
-from .linear import PartialSums, linear_split
+from .base import KVNeed, Mixer, PositionEncoding, build_part, register_part
+from .linear import PartialSums, linear, linear_split
+from .rope import Rope
 
 
 @register_part("mixer", "attention")
@@ -24,7 +32,9 @@ class Attention(Mixer):
     """Parameters: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``,
     ``scale``, ``softcap`` (0 = off), ``window`` (None = all keys), ``position``
     (a PartSpec of category ``position``), ``q_weight``/``k_weight``/``v_weight``/
-    ``o_weight`` (tensor names); optional ``rope_epilogue`` (default false): run the
+    ``o_weight`` (tensor names; ``v_weight`` None or absent: the values are the keys as
+    projected); optional ``qk_norm``: {``q_weight``, ``k_weight`` (tensor names of head_dim
+    values each), ``eps``}; optional ``rope_epilogue`` (default false): run the
     q, k, v projection with the rotary encoding and the cache write in its epilogue
     (``kernels.gemm_tc_rope``) where sizes and encoding allow.  Off by default
     because it measures slower than the projection followed by the rotary kernel:
@@ -51,7 +61,22 @@ class Attention(Mixer):
             raise ConfigError(f"attention: {self.nq} heads are not a multiple of {self.nkv} kv heads")
         pos = self.params.get("position") or PartSpec("none")
         self.position = build_part("position", pos, ctx)
-        self.names = [self.param(k) for k in ("q_weight", "k_weight", "v_weight", "o_weight")]
+        self.names = [self.param("q_weight"), self.param("k_weight"), self.params.get("v_weight"),
+                      self.param("o_weight")]
+        self.v_from_k = self.names[2] is None
+        self.qk_norm = self.params.get("qk_norm")
+        if self.qk_norm is not None:
+            missing = [k for k in ("q_weight", "k_weight", "eps") if k not in self.qk_norm]
+            if missing:
+                raise ConfigError(f"attention: 'qk_norm' needs {missing}")
+        # norm or shared values: the projection is packed by the kernel that norms, rotates and stores,
+        # which knows rotations (a rotary encoding or none) and nothing else that rewrites q and k
+        self.packs = self.v_from_k or self.qk_norm is not None
+        if self.packs and not isinstance(self.position, Rope) \
+                and type(self.position).encode is not PositionEncoding.encode:
+            raise ConfigError(f"attention: qk_norm and shared values go with a rotary encoding or none, "
+                              f"not with '{self.position.kind}'")
+        self.q_norm_w = self.k_norm_w = None
         self.w_qkv = None
         self.w_o = None
         self.rope_epilogue = False
@@ -61,23 +86,31 @@ class Attention(Mixer):
 
     def weight_decls(self):
         q, k, v, o = self.names
-        return [WeightDecl(q, (self.nq * self.hd, self.hidden)),
-                WeightDecl(k, (self.nkv * self.hd, self.hidden)),
-                WeightDecl(v, (self.nkv * self.hd, self.hidden)),
-                WeightDecl(o, (self.hidden, self.nq * self.hd)),
-                *self.position.weight_decls()]
+        decls = [WeightDecl(q, (self.nq * self.hd, self.hidden)),
+                 WeightDecl(k, (self.nkv * self.hd, self.hidden))]
+        if v is not None:
+            decls.append(WeightDecl(v, (self.nkv * self.hd, self.hidden)))
+        decls.append(WeightDecl(o, (self.hidden, self.nq * self.hd)))
+        if self.qk_norm is not None:
+            decls += [WeightDecl(self.qk_norm["q_weight"], (self.hd,), "norm"),
+                      WeightDecl(self.qk_norm["k_weight"], (self.hd,), "norm")]
+        return [*decls, *self.position.weight_decls()]
 
     def load(self, weights):
         q, k, v, o = self.names
         dt = self.ctx.compute_dtype
         # one matrix product for q, k and v: rows [q heads | k heads | v heads]
-        self.w_qkv = torch.cat([weights[q], weights[k], weights[v]], dim=0).to(dt).contiguous()
+        mats = [weights[q], weights[k]] + ([weights[v]] if v is not None else [])
+        self.w_qkv = torch.cat(mats, dim=0).to(dt).contiguous()
         self.w_o = weights[o].to(dt).contiguous()
         self.position.load(weights)
+        if self.qk_norm is not None:
+            self.q_norm_w = weights[self.qk_norm["q_weight"]].to(torch.float32).contiguous()
+            self.k_norm_w = weights[self.qk_norm["k_weight"]].to(torch.float32).contiguous()
         # bfloat16 with a head size and a K that the tensor-core product takes: the rows of every head in the
         # order in which the product's epilogue rotates pairs and writes the cache (used only when the position
         # encoding says, step by step, that it is such a rotation)
-        self.rope_epilogue = (bool(self.params.get("rope_epilogue")) and dt == torch.bfloat16 and self.hd % 32 == 0
+        self.rope_epilogue = (bool(self.params.get("rope_epilogue")) and not self.packs and dt == torch.bfloat16 and self.hd % 32 == 0
                               and self.hidden % 8 == 0 and self.w_qkv.is_cuda
                               and self.position.rotates_half_pairs(self.hd))
         if self.rope_epilogue:
@@ -90,7 +123,7 @@ class Attention(Mixer):
         return 4 if self.ctx.compute_dtype == torch.float32 else 2
 
     def decode_bytes(self, lens) -> int:
-        weights = ((self.nq + 2 * self.nkv) * self.hd * self.hidden + self.hidden * self.nq * self.hd) * self._el()
+        weights = (self.w_qkv.shape[0] * self.hidden + self.hidden * self.nq * self.hd) * self._el()
         kv_row = 2 * self.nkv * self.hd * self._el()
         return weights + sum(kv_row * (min(n, self.window) if self.window else n) for n in lens)
 
@@ -104,7 +137,7 @@ class Attention(Mixer):
 
     def prefill_flops(self, lens) -> int:
         T = sum(lens)
-        proj = 2 * T * ((self.nq + 2 * self.nkv) * self.hd * self.hidden + self.hidden * self.nq * self.hd)
+        proj = 2 * T * (self.w_qkv.shape[0] * self.hidden + self.hidden * self.nq * self.hd)
         return proj + self.score_flops(lens)
 
     def _project_rotate_store(self, x, batch, view):
@@ -126,10 +159,30 @@ class Attention(Mixer):
                              tickets=self.tickets)
         return qkv
 
+    def _project_norm_pack(self, x, batch, view):
+        """The projection in 32-bit rows; q and k heads normed and rotated, the values taken
+        (from the keys as projected, or their own heads), all packed and the cache written: one kernel."""
+        nq, nkv, hd = self.nq, self.nkv, self.hd
+        proj = linear(x, self.w_qkv, out_dtype=torch.float32)
+        qkv = torch.empty(x.shape[0], (nq + 2 * nkv) * hd, dtype=x.dtype, device=x.device)
+        rope = self.position if isinstance(self.position, Rope) else None
+        if rope is not None and rope.rotary_dim > hd:
+            raise ConfigError(f"rope: rotary_dim {rope.rotary_dim} exceeds head_dim {hd}")
+        kernels.qk_norm_rope_store(
+            qkv, proj, batch, nq, nkv, hd,
+            rope.inv_freq if rope is not None else kernels.no_frequencies(x.device),
+            rope.rotary_dim if rope is not None else 0, rope.pairing if rope is not None else "half",
+            q_weight=self.q_norm_w, k_weight=self.k_norm_w,
+            eps=float(self.qk_norm["eps"]) if self.qk_norm is not None else 0.0,
+            v_from_k=self.v_from_k, kv=view.kv if view.writes else None)
+        return qkv
+
     def forward(self, x, batch, view):
         nq, nkv, hd = self.nq, self.nkv, self.hd
         kv = view.kv
-        if self.rope_epilogue:
+        if self.packs:
+            qkv = self._project_norm_pack(x, batch, view)
+        elif self.rope_epilogue:
             qkv = self._project_rotate_store(x, batch, view)
         else:
             qkv = linear_split(x, self.w_qkv)

@@ -138,6 +138,15 @@ class Norm(Part):
         also returns then.forward(x) in ``out_dtype``."""
         raise NotImplementedError
 
+    def after_add(self, x, a, out_dtype):
+        """x += a in place (32-bit sum; ``a`` a tensor, partial sums or a weighted
+        sum of them), then this norm of the new x in ``out_dtype``.  A norm with a
+        kernel that does both overrides this."""
+        from .. import kernels
+        from .linear import as_terms
+        kernels.add_scaled_rmsnorm(x, as_terms(a))
+        return self.forward(x, out_dtype)
+
 
 class PositionEncoding(Part):
     """How a mixer's queries and keys learn their positions.  An encoding may
@@ -190,7 +199,8 @@ class Mixer(Part):
 
     def forward(self, x, batch, view):
         """x [T, H] in the compute dtype (normalised) -> [T, H] in the compute
-        dtype, or a :class:`~airframe_b200.parts.linear.PartialSums` of it.  ``batch`` is the :class:`~airframe_b200.engine.batch.StepBatch`,
+        dtype, or a :class:`~airframe_b200.parts.linear.PartialSums` or
+        :class:`~airframe_b200.parts.linear.WeightedSum` of it.  ``batch`` is the :class:`~airframe_b200.engine.batch.StepBatch`,
         ``view`` the layer's :class:`~airframe_b200.cache.LayerCacheView`.
 
         A captured decode step is padded to a fixed number of rows: padding
@@ -202,6 +212,10 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    # False for the kind that stands for "this layer has no feed-forward": a block then leaves the
+    # sublayer out altogether (and wants no norm for it)
+    present = True
+
     def forward(self, x, batch):
         """x [T, H] compute dtype -> [T, H] compute dtype."""
         raise NotImplementedError

@@ -4,17 +4,16 @@
 and after both halves (reference order
 ``src/backend/bindless/pipeline/inference.rs:1096-1251``, net effect
 x + norm(a) of ``sh_layer_v1.wgsl:834-849,869-884``).
-``prenorm``: x += mixer(pre(x)); x += ff(pre(x)).
+``prenorm``: x += mixer(pre(x)); x += ff(pre(x)); a layer whose feed-forward
+is of the kind ``none`` has the first half only.  Each residual sum is one
+kernel with the norm that follows it (the feed-forward's, or the next layer's
+first).
 """
 from __future__ import annotations
 
 from .. import kernels
 from .base import Block, register_part
-from .linear import PartialSums
-
-
-def _dense(a):
-    return a.parts if isinstance(a, PartialSums) else a
+from .linear import as_terms
 
 
 @register_part("block", "sandwich")
@@ -41,13 +40,27 @@ class SandwichBlock(Block):
 class PreNormBlock(Block):
     roles = ("pre_mixer", "pre_feed_forward")
 
+    def __init__(self, params, ctx, mixer, feed_forward, norms):
+        if not feed_forward.present:
+            self.roles = ("pre_mixer",)
+        super().__init__(params, ctx, mixer, feed_forward, norms)
+
+    def _add(self, x, a, then, dt):
+        """x += a; returns then(x) when a norm follows."""
+        if then is not None:
+            return then.after_add(x, a, dt)
+        kernels.add_scaled_rmsnorm(x, as_terms(a))
+        return None
+
     def forward(self, x, batch, view, normed=None, next_pre=None):
         n = self.norms
         dt = self.ctx.compute_dtype
         h = normed if normed is not None else n["pre_mixer"].forward(x, dt)
-        kernels.add_(x, _dense(self.mixer.forward(h, batch, view)))
-        kernels.add_(x, _dense(self.feed_forward.forward(n["pre_feed_forward"].forward(x, dt), batch)))
-        return next_pre.forward(x, dt) if next_pre is not None else None
+        a = self.mixer.forward(h, batch, view)
+        if not self.feed_forward.present:
+            return self._add(x, a, next_pre, dt)
+        h = self._add(x, a, n["pre_feed_forward"], dt)
+        return self._add(x, self.feed_forward.forward(h, batch), next_pre, dt)
 
     def first_norm(self):
         return self.norms["pre_mixer"]

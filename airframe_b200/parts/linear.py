@@ -37,6 +37,30 @@ class PartialSums:
         return self.parts.shape[1:]
 
 
+class WeightedSum:
+    """A mixer's result as a sum that is still to be taken: ``terms`` is a list
+    of (tensor or :class:`PartialSums`, scale).  The consumer (a block's residual
+    sum) adds scale * term for every term in 32 bits, so that no term is rounded
+    to the compute dtype on its way into the residual stream."""
+
+    def __init__(self, terms):
+        self.terms = list(terms)
+
+    @property
+    def shape(self):
+        return self.terms[0][0].shape
+
+
+def as_terms(a) -> list:
+    """(tensor, scale) pairs of a part's result, whatever form it came in:
+    a tensor [T, H], float32 partial sums [S, T, H], or a weighted sum of those."""
+    if isinstance(a, WeightedSum):
+        return [(t.parts if isinstance(t, PartialSums) else t, float(s)) for t, s in a.terms]
+    if isinstance(a, PartialSums):
+        return [(a.parts, 1.0)]
+    return [(a, 1.0)]
+
+
 def linear_split(x, w):
     """x w^T for few rows and a long K: split-K partial sums when that fills
     the GPU better, else the plain result.  Returns a tensor or PartialSums."""

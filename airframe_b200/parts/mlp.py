@@ -60,3 +60,14 @@ class GatedMlp(FeedForward):
     def forward(self, x, batch):
         h = gated_linear(x, self.w_gu, self.inter, self.activation, self.interleaved)
         return linear_split(h, self.w_down)
+
+
+@register_part("feed_forward", "none")
+class NoFeedForward(FeedForward):
+    """A layer without a feed-forward: a block that knows of it leaves the
+    sublayer and its norm out (``prenorm`` does)."""
+    graph_safe = True
+    present = False
+
+    def forward(self, x, batch):
+        raise ConfigError("a layer without a feed-forward was asked to run one (its block does not leave it out)")

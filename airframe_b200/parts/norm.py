@@ -12,7 +12,7 @@ import torch
 from .. import kernels
 from ..weights.loader import WeightDecl
 from .base import Norm, register_part
-from .linear import PartialSums
+from .linear import PartialSums, as_terms
 
 
 @register_part("norm", "rms_norm")
@@ -58,4 +58,11 @@ class RmsNorm(Norm):
         kernels.add_rmsnorm(x, a, self.w, self.eps, self.offset, y=y,
                             w_next=then.w if then is not None else None,
                             eps_next=then.eps if then is not None else 0.0, n_parts=n_parts)
+        return y
+
+    def after_add(self, x, a, out_dtype):
+        """x += a (a tensor, partial sums or a weighted sum of them) and this norm
+        of the new x, in one kernel."""
+        y = torch.empty(x.shape[0], self.size, dtype=out_dtype, device=x.device)
+        kernels.add_scaled_rmsnorm(x, as_terms(a), y=y, w_next=self.w, eps=self.eps, offset=self.offset)
         return y

@@ -1,0 +1,233 @@
+"""Mixers that keep a state of fixed size per sequence instead of keys and
+values.  The state lives in the cache's per-sequence state (32-bit floats, zero
+when a sequence starts) and is carried from step to step; a prompt in one step
+and the same tokens one by one run the same recurrence token after token.
+
+``general_delta``: the generalized delta rule.  Per head, with r, k, v of the
+token, a decay w per key channel, a removal rate a per key channel and the unit
+key u = k / sqrt(|k|^2 + key_eps):
+
+    S <- diag(w) S - (a * u)(u^T S) + k v^T        o = S^T r
+
+(both terms read the old S).  w = exp(-decay_scale * sigmoid(W2 tanh(W1 h) + w0)),
+a = sigmoid(Wa h + ba).  Each head's o is divided by its root mean square, times a
+plain weight, times sigmoid(Wg h), then the output projection.
+
+``lightning_attention``: linear attention with a fixed decay per head:
+q, k, v = silu of their projections, S <- decay_h S + k v^T, o = S^T q; the heads
+together are RMS-normed with a plain weight, times sigmoid(Wg h), then projected.
+
+``mingru``: a gated recurrence over a vector: z = sigmoid(Wz h + bz),
+c = Wx h + bx, candidate = c + 1/2 where c >= 0 and sigmoid(c) below,
+S <- (1 - z) S + z * candidate, output Wo (S * silu(Wg h)).
+
+Every projection of a mixer is one product into 32-bit rows; what enters a
+recurrence (decays, gates, unit keys) is worked out in 32 bits from them.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .. import kernels
+from ..config.base import ConfigError
+from ..weights.loader import WeightDecl
+from .base import Mixer, StateNeed, register_part
+from .linear import linear, linear_split
+
+
+def _el(ctx) -> int:
+    return 4 if ctx.compute_dtype == torch.float32 else 2
+
+
+class _StateMixer(Mixer):
+    """What the three have in common: named tensors, one packed projection."""
+    graph_safe = True
+
+    def _names(self, roles):
+        names = self.param("weights")
+        missing = [r for r in roles if r not in names]
+        if missing:
+            raise ConfigError(f"{self.kind}: parameter 'weights' names no tensor for {missing}")
+        return {r: names[r] for r in roles}
+
+    def _pack(self, weights, roles):
+        """The rows of the named matrices one under the other (each section padded to a multiple
+        of four rows so that sections of 32-bit output rows start on 16 bytes) and where each starts."""
+        dt = self.ctx.compute_dtype
+        mats, offsets, at = [], {}, 0
+        for r in roles:
+            w = weights[self.names[r]].to(dt)
+            offsets[r] = at
+            pad = (-w.shape[0]) % 4
+            if pad:
+                w = torch.cat([w, torch.zeros(pad, w.shape[1], dtype=dt, device=w.device)])
+            mats.append(w)
+            at += w.shape[0]
+        return torch.cat(mats, dim=0).contiguous(), offsets
+
+
+@register_part("mixer", "general_delta")
+class GeneralDelta(_StateMixer):
+    """Parameters: ``hidden_size``, ``num_heads``, ``head_dim`` (keys and values),
+    ``eps`` (of the output norm), ``weights``: tensor names for ``r, k, v, g, a, a_bias,
+    w1, w2, w0, norm, o``; optional ``decay_rank`` (rows of w1; read from the tensor when
+    absent), ``decay_scale`` (default exp(-1/2)), ``key_eps`` (default 1e-6)."""
+    ROLES = ("r", "k", "v", "g", "a", "a_bias", "w1", "w2", "w0", "norm", "o")
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.hidden = int(self.param("hidden_size"))
+        self.heads = int(self.param("num_heads"))
+        self.hd = int(self.param("head_dim"))
+        self.eps = float(self.param("eps"))
+        rank = self.params.get("decay_rank")
+        self.rank = int(rank) if rank is not None else None
+        self.decay_scale = float(self.params.get("decay_scale", math.exp(-0.5)))
+        self.key_eps = float(self.params.get("key_eps", 1e-6))
+        self.names = self._names(self.ROLES)
+        self.n = self.heads * self.hd
+
+    def state_need(self):
+        return StateNeed((self.heads, self.hd, self.hd), "float32")      # [head][value column][key channel]
+
+    def weight_decls(self):
+        n, h, nm = self.n, self.hidden, self.names
+        return [*(WeightDecl(nm[r], (n, h)) for r in ("r", "k", "v", "g", "a")),
+                WeightDecl(nm["a_bias"], (n,), "norm"), WeightDecl(nm["w1"], (self.rank, h)),
+                WeightDecl(nm["w2"], (n, self.rank)), WeightDecl(nm["w0"], (n,), "norm"),
+                WeightDecl(nm["norm"], (n,), "norm"), WeightDecl(nm["o"], (h, n))]
+
+    def load(self, weights):
+        nm = self.names
+        self.rank = weights[nm["w1"]].shape[0]
+        if weights[nm["w2"]].shape[1] != self.rank:
+            raise ConfigError(f"general_delta: {nm['w1']} has {self.rank} rows, {nm['w2']} has "
+                              f"{weights[nm['w2']].shape[1]} columns")
+        self.w_in, self.off = self._pack(weights, ("r", "k", "v", "g", "a", "w1"))
+        f32 = torch.float32
+        self.a_bias = weights[nm["a_bias"]].to(f32).contiguous()
+        self.w0 = weights[nm["w0"]].to(f32).contiguous()
+        self.w2 = weights[nm["w2"]].to(f32).contiguous()
+        self.norm_w = weights[nm["norm"]].to(f32).contiguous()
+        self.w_o = weights[nm["o"]].to(self.ctx.compute_dtype).contiguous()
+
+    def decode_bytes(self, lens) -> int:
+        weights = (self.w_in.numel() + self.w_o.numel()) * _el(self.ctx) + 4 * self.w2.numel()
+        return weights + len(lens) * 2 * 4 * self.heads * self.hd * self.hd      # the state, read and written
+
+    def prefill_flops(self, lens) -> int:
+        T = sum(lens)
+        return 2 * T * (self.w_in.numel() + self.w_o.numel()) + T * self.heads * 7 * self.hd * self.hd
+
+    def forward(self, x, batch, view):
+        T, n, off = x.shape[0], self.n, self.off
+        proj = linear(x, self.w_in, out_dtype=torch.float32)
+        pre = torch.empty(T, 3, n, dtype=torch.float32, device=x.device)
+        kernels.delta_prep(pre, proj, off["k"], off["a"], off["w1"], self.a_bias, self.w0, self.w2, self.heads,
+                           self.hd, self.decay_scale, self.key_eps)
+        o = torch.empty(T, n, dtype=torch.float32, device=x.device)
+        kernels.state_scan("delta", o, proj[:, off["r"]: off["r"] + n], proj[:, off["k"]: off["k"] + n],
+                           proj[:, off["v"]: off["v"] + n], view.state, batch, self.heads, self.hd, self.hd,
+                           w=pre[:, 0], u=pre[:, 1], au=pre[:, 2])
+        y = torch.empty(T, n, dtype=x.dtype, device=x.device)
+        kernels.gated_group_norm(y, o, self.norm_w, proj[:, off["g"]: off["g"] + n], self.hd, self.eps)
+        return linear_split(y, self.w_o)
+
+
+@register_part("mixer", "lightning_attention")
+class LightningAttention(_StateMixer):
+    """Parameters: ``hidden_size``, ``num_heads``, ``head_dim`` (queries and keys),
+    ``value_dim``, ``decay`` (one factor per head), ``eps`` (of the output norm),
+    ``weights``: tensor names for ``q, k, v, g, norm, o``."""
+    ROLES = ("q", "k", "v", "g", "norm", "o")
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.hidden = int(self.param("hidden_size"))
+        self.heads = int(self.param("num_heads"))
+        self.dk = int(self.param("head_dim"))
+        self.dv = int(self.param("value_dim"))
+        self.eps = float(self.param("eps"))
+        decay = self.param("decay")
+        if not isinstance(decay, (list, tuple)) or len(decay) != self.heads:
+            raise ConfigError(f"lightning_attention: 'decay' must list one factor for each of the {self.heads} heads")
+        self.decay_host = torch.tensor([float(d) for d in decay], dtype=torch.float64).to(torch.float32)
+        self.names = self._names(self.ROLES)
+
+    def state_need(self):
+        return StateNeed((self.heads, self.dv, self.dk), "float32")
+
+    def weight_decls(self):
+        nk, nv, h, nm = self.heads * self.dk, self.heads * self.dv, self.hidden, self.names
+        return [WeightDecl(nm["q"], (nk, h)), WeightDecl(nm["k"], (nk, h)), WeightDecl(nm["v"], (nv, h)),
+                WeightDecl(nm["g"], (nv, h)), WeightDecl(nm["norm"], (nv,), "norm"), WeightDecl(nm["o"], (h, nv))]
+
+    def load(self, weights):
+        nm = self.names
+        self.w_in, self.off = self._pack(weights, ("q", "k", "v", "g"))
+        self.norm_w = weights[nm["norm"]].to(torch.float32).contiguous()
+        self.w_o = weights[nm["o"]].to(self.ctx.compute_dtype).contiguous()
+        self.decay = self.decay_host.to(self.ctx.device)
+
+    def decode_bytes(self, lens) -> int:
+        return ((self.w_in.numel() + self.w_o.numel()) * _el(self.ctx)
+                + len(lens) * 2 * 4 * self.heads * self.dk * self.dv)
+
+    def prefill_flops(self, lens) -> int:
+        T = sum(lens)
+        return 2 * T * (self.w_in.numel() + self.w_o.numel()) + T * self.heads * 4 * self.dk * self.dv
+
+    def forward(self, x, batch, view):
+        T, off = x.shape[0], self.off
+        nk, nv = self.heads * self.dk, self.heads * self.dv
+        proj = linear(x, self.w_in, out_dtype=torch.float32)
+        o = torch.empty(T, nv, dtype=torch.float32, device=x.device)
+        kernels.state_scan("decay", o, proj[:, off["q"]: off["q"] + nk], proj[:, off["k"]: off["k"] + nk],
+                           proj[:, off["v"]: off["v"] + nv], view.state, batch, self.heads, self.dk, self.dv,
+                           decay=self.decay, silu=True)
+        y = torch.empty(T, nv, dtype=x.dtype, device=x.device)
+        kernels.gated_group_norm(y, o, self.norm_w, proj[:, off["g"]: off["g"] + nv], nv, self.eps)
+        return linear_split(y, self.w_o)
+
+
+@register_part("mixer", "mingru")
+class MinGru(_StateMixer):
+    """Parameters: ``hidden_size``, ``width`` (of the state), ``weights``: tensor
+    names for ``z, z_bias, x, x_bias, g, o``."""
+    ROLES = ("z", "z_bias", "x", "x_bias", "g", "o")
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.hidden = int(self.param("hidden_size"))
+        self.width = int(self.param("width"))
+        self.names = self._names(self.ROLES)
+
+    def state_need(self):
+        return StateNeed((self.width,), "float32")
+
+    def weight_decls(self):
+        w, h, nm = self.width, self.hidden, self.names
+        return [WeightDecl(nm["z"], (w, h)), WeightDecl(nm["z_bias"], (w,), "norm"), WeightDecl(nm["x"], (w, h)),
+                WeightDecl(nm["x_bias"], (w,), "norm"), WeightDecl(nm["g"], (w, h)), WeightDecl(nm["o"], (h, w))]
+
+    def load(self, weights):
+        nm = self.names
+        self.w_in, self.off = self._pack(weights, ("z", "x", "g"))
+        self.z_bias = weights[nm["z_bias"]].to(torch.float32).contiguous()
+        self.x_bias = weights[nm["x_bias"]].to(torch.float32).contiguous()
+        self.w_o = weights[nm["o"]].to(self.ctx.compute_dtype).contiguous()
+
+    def decode_bytes(self, lens) -> int:
+        return (self.w_in.numel() + self.w_o.numel()) * _el(self.ctx) + len(lens) * 2 * 4 * self.width
+
+    def prefill_flops(self, lens) -> int:
+        return 2 * sum(lens) * (self.w_in.numel() + self.w_o.numel())
+
+    def forward(self, x, batch, view):
+        off = self.off
+        proj = linear(x, self.w_in, out_dtype=torch.float32)
+        y = torch.empty(x.shape[0], self.width, dtype=x.dtype, device=x.device)
+        kernels.gated_scan(y, proj, off["z"], off["x"], off["g"], self.z_bias, self.x_bias, view.state, batch)
+        return linear_split(y, self.w_o)

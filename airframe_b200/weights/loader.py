@@ -26,11 +26,18 @@ from .safetensors_io import SafetensorsError, SafetensorsFile
 class WeightDecl:
     """A tensor that a part needs.  ``kind`` tells the random-weights mode how
     to fill it: ``matrix`` and ``table`` N(0, 0.02), ``norm`` N(0, 0.1),
-    ``int_table`` integers."""
+    ``int_table`` integers.  A ``None`` in ``shape`` stands for a size that only
+    the stored tensor gives (the part reads it when it loads)."""
     name: str
     shape: tuple
     kind: str = "matrix"
     optional: bool = False
+
+
+def shape_fits(declared, got) -> bool:
+    """Whether a stored shape is the declared one (None: any size)."""
+    declared, got = tuple(declared), tuple(got)
+    return len(declared) == len(got) and all(d is None or d == g for d, g in zip(declared, got))
 
 
 class WeightError(ValueError):
@@ -124,7 +131,7 @@ def load_weights(source, decls, compute_dtype: torch.dtype, device) -> dict:
     for n, d in declared.items():
         if n in have:
             _, shape = source.info(n)
-            if tuple(shape) != tuple(d.shape):
+            if not shape_fits(d.shape, shape):
                 wrong.append((n, tuple(d.shape), tuple(shape)))
     if missing or unexpected or wrong:
         raise WeightError(source.describe(), missing, unexpected, wrong)

@@ -29,6 +29,9 @@ def tensor_seed(seed: int, name: str) -> int:
 def random_tensor(decl: WeightDecl, seed: int, dtype: torch.dtype, device="cpu") -> torch.Tensor:
     """The tensor of ``decl`` for ``seed``.  Values depend on the device kind
     (the CPU and CUDA generators differ); folders are always written from the CPU."""
+    if any(n is None for n in decl.shape):
+        raise ValueError(f"tensor '{decl.name}': a size that only a stored tensor gives is open; random weights "
+                         "need it named in the configuration")
     gen = torch.Generator(device=device)
     gen.manual_seed(tensor_seed(seed, decl.name))
     if decl.kind == "int_table":
