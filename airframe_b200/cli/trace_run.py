@@ -52,7 +52,9 @@ def main(argv=None, stdin=None, stdout=None) -> int:
     out_dir = Path(args.out)
     out_dir.mkdir(parents=True, exist_ok=True)
     limit = config_from_folder(args.model).model_spec().max_positions
-    rt = GpuRuntime.load(args.model, dtype=args.dtype, device=args.device, max_tokens=args.max_tokens,
+    # the cache holds whole pages a sequence: up to a page less one token of slack for each of up to 64 live requests
+    slack = (kernels.PAGE - 1) * min(args.max_tokens, 64)
+    rt = GpuRuntime.load(args.model, dtype=args.dtype, device=args.device, max_tokens=args.max_tokens + slack,
                          max_context=limit)
     slots: dict = {}
     for line in stdin:

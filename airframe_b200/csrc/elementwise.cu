@@ -515,6 +515,83 @@ add_scaled_rmsnorm_kernel(float* __restrict__ x, const void* __restrict__ a, int
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) yr[i] = from_f32<TY>(row[i] * inv * (offset + w_next[i]));
 }
 
+// The same for rows of up to 8192 values with hidden % 4 == 0: a thread owns NV groups of four values, every
+// load is issued before the first reduction, and the norm's weight is asked for before the wait for the kernel in front.
+__device__ __forceinline__ void term_group(float* acc, float scale, const void* p, int dtype, int n_parts,
+                                           size_t part_stride, size_t at) {
+  if (dtype == AF_BF16) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(p) + at);
+    acc[0] += scale * __uint_as_float(raw.x << 16);
+    acc[1] += scale * __uint_as_float(raw.x & 0xffff0000u);
+    acc[2] += scale * __uint_as_float(raw.y << 16);
+    acc[3] += scale * __uint_as_float(raw.y & 0xffff0000u);
+    return;
+  }
+  const float* f = static_cast<const float*>(p) + at;
+  float v[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int p0 = 0; p0 < n_parts; p0 += 8) {
+    float4 t[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      t[u] = p0 + u < n_parts ? *reinterpret_cast<const float4*>(f + (size_t)(p0 + u) * part_stride)
+                              : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v[0] += t[u].x, v[1] += t[u].y, v[2] += t[u].z, v[3] += t[u].w;
+  }
+#pragma unroll
+  for (int u = 0; u < 4; ++u) acc[u] += scale * v[u];
+}
+
+template <typename TY, int NV>
+__global__ void __launch_bounds__(1024)
+add_scaled_rmsnorm_row_kernel(float* __restrict__ x, const void* __restrict__ a, int a_dtype, int a_parts, float scale_a,
+                              const void* __restrict__ b, int b_dtype, int b_parts, float scale_b, size_t part_stride,
+                              TY* __restrict__ y, const float* __restrict__ w_next, int hidden, float eps, float offset) {
+  pdl_launch_dependents();
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  float wn[NV][4], xv[NV][4];
+  bool on[NV];
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const int i = (threadIdx.x + v * blockDim.x) * 4;
+    on[v] = i < hidden;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) wn[v][u] = xv[v][u] = 0.f;
+    if (on[v] && y != nullptr) {
+      const float4 t = *reinterpret_cast<const float4*>(w_next + i);
+      wn[v][0] = t.x, wn[v][1] = t.y, wn[v][2] = t.z, wn[v][3] = t.w;
+    }
+  }
+  pdl_wait();
+  a = pdl_fresh(a);
+  b = pdl_fresh(b);
+  x = pdl_fresh(x);
+  float ss = 0.f;
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    if (!on[v]) continue;
+    const size_t at = (size_t)r * hidden + (threadIdx.x + v * blockDim.x) * 4;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const float4 xt = *reinterpret_cast<const float4*>(x + at);
+    term_group(acc, scale_a, a, a_dtype, a_parts, part_stride, at);
+    if (b != nullptr) term_group(acc, scale_b, b, b_dtype, b_parts, part_stride, at);
+    xv[v][0] = xt.x + acc[0], xv[v][1] = xt.y + acc[1], xv[v][2] = xt.z + acc[2], xv[v][3] = xt.w + acc[3];
+    *reinterpret_cast<float4*>(x + at) = make_float4(xv[v][0], xv[v][1], xv[v][2], xv[v][3]);
+    ss += xv[v][0] * xv[v][0] + xv[v][1] * xv[v][1] + xv[v][2] * xv[v][2] + xv[v][3] * xv[v][3];
+  }
+  if (y == nullptr) return;
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)hidden + eps);
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    if (!on[v]) continue;
+    TY* yr = y + (size_t)r * hidden + (threadIdx.x + v * blockDim.x) * 4;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) yr[u] = from_f32<TY>(xv[v][u] * inv * (offset + wn[v][u]));
+  }
+}
+
 AF_EXPORT int af_add_scaled_rmsnorm(float* x, const void* a, int a_dtype, int a_parts, float scale_a, const void* b,
                                     int b_dtype, int b_parts, float scale_b, void* y, int y_dtype, const float* w_next,
                                     int n_rows, int hidden, float eps, float offset, cudaStream_t stream) {
@@ -526,6 +603,23 @@ AF_EXPORT int af_add_scaled_rmsnorm(float* x, const void* a, int a_dtype, int a_
   AF_REQUIRE((size_t)hidden * sizeof(float) <= 48 * 1024, "af_add_scaled_rmsnorm: rows of up to 12288 values");
   AF_REQUIRE(y == nullptr || w_next != nullptr, "af_add_scaled_rmsnorm: a norm needs its weight");
   const size_t part_stride = (size_t)n_rows * hidden;
+  if (hidden % 4 == 0 && hidden <= 8192 &&
+      (((uintptr_t)x | (uintptr_t)a | (uintptr_t)b | (uintptr_t)w_next | (uintptr_t)y) & 15) == 0) {
+    const int nv = hidden > 4096 ? 2 : 1;
+    const int threads = ((hidden / (4 * nv) + 31) / 32) * 32;
+    if (nv == 2) {
+      AF_DISPATCH_DTYPE(y_dtype, TY,
+                        af_launch(add_scaled_rmsnorm_row_kernel<TY, 2>, dim3(n_rows), dim3(threads), 0, stream, x, a, a_dtype,
+                                  a_parts, scale_a, b, b_dtype, b_parts, scale_b, part_stride, (TY*)y, w_next, hidden, eps,
+                                  offset));
+    } else {
+      AF_DISPATCH_DTYPE(y_dtype, TY,
+                        af_launch(add_scaled_rmsnorm_row_kernel<TY, 1>, dim3(n_rows), dim3(threads), 0, stream, x, a, a_dtype,
+                                  a_parts, scale_a, b, b_dtype, b_parts, scale_b, part_stride, (TY*)y, w_next, hidden, eps,
+                                  offset));
+    }
+    AF_CHECK_LAUNCH("af_add_scaled_rmsnorm");
+  }
   AF_DISPATCH_DTYPE(y_dtype, TY,
                     af_launch(add_scaled_rmsnorm_kernel<TY>, dim3(n_rows), dim3(256), (size_t)hidden * sizeof(float), stream,
                               x, a, a_dtype, a_parts, scale_a, b, b_dtype, b_parts, scale_b, part_stride, (TY*)y, w_next,

@@ -16,51 +16,65 @@
 //   unit key   u = k / sqrt(sum_c k^2 + key_eps)
 //   decay      w = exp(-decay_scale * sigmoid(w2 . tanh(w1 row) + w0))
 //   removal    au = sigmoid(a + a_bias) * u
-// written as float rows [token][3][heads * dk] (w, u, au).  One block per token, a warp per head.
-__global__ void __launch_bounds__(128)
+// written as float rows [token][3][heads * dk] (w, u, au).  One block per (token, head), a thread per key
+// channel; `w2t` is the second low-rank matrix transposed, [rank][heads * dk], so that the threads of a
+// block read it side by side.
+__global__ void __launch_bounds__(256)
 delta_prep_kernel(float* __restrict__ out, const float* __restrict__ proj, long long ld, int off_k, int off_a,
                   int off_w1, const float* __restrict__ a_bias, const float* __restrict__ w0,
-                  const float* __restrict__ w2, int rank, int heads, int dk, float decay_scale, float key_eps) {
+                  const float* __restrict__ w2t, int rank, int heads, int dk, float decay_scale, float key_eps) {
   pdl_launch_dependents();
-  pdl_wait();
   extern __shared__ float low[];                // tanh of the low-rank row
-  const int t = blockIdx.x;
+  __shared__ float scratch[33];
+  const int t = blockIdx.x, h = blockIdx.y;
+  const int n = heads * dk;
+  // (weights before the wait for the projection)
+  float bias_a[4], bias_w[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const int c = threadIdx.x + e * blockDim.x;
+    bias_a[e] = c < dk ? a_bias[h * dk + c] : 0.f;
+    bias_w[e] = c < dk ? w0[h * dk + c] : 0.f;
+  }
+  pdl_wait();
   const float* row = proj + (size_t)t * ld;
   for (int l = threadIdx.x; l < rank; l += blockDim.x) low[l] = tanhf(row[off_w1 + l]);
-  __syncthreads();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
-  const int n = heads * dk;
+  float kv[4], av[4], ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const int c = threadIdx.x + e * blockDim.x;
+    kv[e] = c < dk ? row[off_k + h * dk + c] : 0.f;
+    av[e] = c < dk ? row[off_a + h * dk + c] : 0.f;
+    ss += kv[e] * kv[e];
+  }
+  ss = block_sum(ss, scratch);                  // (its barriers also publish `low`)
+  const float nrm = sqrtf(ss + key_eps);
   float* o = out + (size_t)t * 3 * n;
-  for (int h = warp; h < heads; h += nwarp) {
-    float ss = 0.f;
-    for (int c = lane; c < dk; c += 32) {
-      const float kv = row[off_k + h * dk + c];
-      ss += kv * kv;
-    }
-    ss = warp_sum(ss);
-    const float nrm = sqrtf(ss + key_eps);
-    for (int c = lane; c < dk; c += 32) {
-      const int i = h * dk + c;
-      float z = w0[i];
-      const float* wr = w2 + (size_t)i * rank;
-      for (int l = 0; l < rank; ++l) z += low[l] * wr[l];
-      const float sig = 1.f / (1.f + expf(-z));
-      const float u = row[off_k + i] / nrm;
-      const float a = 1.f / (1.f + expf(-(row[off_a + i] + a_bias[i])));
-      o[i] = expf(-decay_scale * sig);
-      o[n + i] = u;
-      o[2 * n + i] = a * u;
-    }
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const int c = threadIdx.x + e * blockDim.x;
+    if (c >= dk) continue;
+    const int i = h * dk + c;
+    float z = bias_w[e];
+    for (int l = 0; l < rank; ++l) z += low[l] * w2t[(size_t)l * n + i];
+    const float sig = 1.f / (1.f + expf(-z));
+    const float u = kv[e] / nrm;
+    const float a = 1.f / (1.f + expf(-(av[e] + bias_a[e])));
+    o[i] = expf(-decay_scale * sig);
+    o[n + i] = u;
+    o[2 * n + i] = a * u;
   }
 }
 
 AF_EXPORT int af_delta_prep(float* out, const float* proj, long long ld, int off_k, int off_a, int off_w1,
-                            const float* a_bias, const float* w0, const float* w2, int rank, int n_tokens, int heads,
+                            const float* a_bias, const float* w0, const float* w2t, int rank, int n_tokens, int heads,
                             int dk, float decay_scale, float key_eps, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
-  AF_REQUIRE(n_tokens > 0 && heads > 0 && dk > 0 && rank > 0 && rank <= 8192, "af_delta_prep: bad sizes");
-  af_launch(delta_prep_kernel, dim3(n_tokens), dim3(128), (size_t)rank * sizeof(float), stream, out, proj, ld, off_k,
-            off_a, off_w1, a_bias, w0, w2, rank, heads, dk, decay_scale, key_eps);
+  AF_REQUIRE(n_tokens > 0 && heads > 0 && heads < 65536 && dk > 0 && dk <= 1024 && rank > 0 && rank <= 8192,
+             "af_delta_prep: bad sizes (key size up to 1024, rank up to 8192)");
+  const int threads = dk <= 32 ? 32 : dk <= 64 ? 64 : dk <= 128 ? 128 : 256;
+  af_launch(delta_prep_kernel, dim3(n_tokens, heads), dim3(threads), (size_t)rank * sizeof(float), stream, out, proj, ld,
+            off_k, off_a, off_w1, a_bias, w0, w2t, rank, heads, dk, decay_scale, key_eps);
   AF_CHECK_LAUNCH("af_delta_prep");
 }
 
@@ -90,12 +104,13 @@ struct AfScanArgs {
 };
 
 #define AF_SCAN_PREFETCH 24    // values a thread holds in registers for the chunk after the current one
+#define AF_SCAN_VEC_ITEMS 2    // the same in 16-byte pieces, per vector, where the sizes allow whole pieces
 
 // One block per (column tile, head, sequence); thread = (column, lane of the column).  The block walks
 // the sequence's tokens in chunks: while it scans a chunk out of shared memory, the next chunk's vectors
 // are on their way into registers.  Key channel c lives at (c / R) (R + 4) + c % R of a staged vector (four
 // floats of padding per lane's run keep the 16-byte reads of a quarter warp in different banks).
-template <int R, int MODE>
+template <int R, int MODE, bool VEC>
 __global__ void __launch_bounds__(256)
 state_scan_kernel(AfScanArgs a) {
   pdl_launch_dependents();
@@ -120,54 +135,171 @@ state_scan_kernel(AfScanArgs a) {
       if (j0 + tid % CT < dv) a.out[(size_t)t * a.out_ts + h * dv + j0 + tid % CT] = 0.f;
     return;
   }
-  for (int i = tid; i < 2 * buf_floats; i += nthr) smem[i] = 0.f;        // (the padding stays zero for good)
-  // the state's piece of this thread
+  // the state's piece of this thread (16-byte pieces where the key size allows)
   float S[R];
   float* st = a.state + (((size_t)slot * a.heads + h) * dv + (col_on ? j : 0)) * dk + part * R;
+  const bool vec = (dk & 3) == 0;
+  if (vec) {
 #pragma unroll
-  for (int i = 0; i < R; ++i) S[i] = (col_on && part * R + i < dk) ? st[i] : 0.f;
+    for (int i = 0; i < R; i += 4) {
+      float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (col_on && part * R + i < dk) q = *reinterpret_cast<const float4*>(st + i);
+      S[i] = q.x, S[i + 1] = q.y, S[i + 2] = q.z, S[i + 3] = q.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < R; ++i) S[i] = (col_on && part * R + i < dk) ? st[i] : 0.f;
+  }
   const float dec = MODE == AF_SCAN_DECAY ? a.decay[h] : 0.f;
-
-  float pf[AF_SCAN_PREFETCH];
-  auto fetch = [&](int t0, int n) {                          // tokens t0 .. t0 + n - 1 into registers
+  auto keep_state = [&]() {
+    if (!col_on) return;
+    if (vec) {
 #pragma unroll
-    for (int e = 0; e < AF_SCAN_PREFETCH; ++e) {
+      for (int i = 0; i < R; i += 4)
+        if (part * R + i < dk) *reinterpret_cast<float4*>(st + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < R; ++i)
+        if (part * R + i < dk) st[i] = S[i];
+    }
+  };
+
+  if (last - first == 1) {
+    // One token (a decode step): its vectors go from memory to the lanes' registers, nothing is staged.
+    const size_t t = (size_t)first;
+    const int c0 = part * R;
+    auto piece = [&](const float* p, float* dst, bool act) {
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        float x = c0 + i < dk ? p[h * dk + c0 + i] : 0.f;
+        dst[i] = act ? x / (1.f + expf(-x)) : x;
+      }
+    };
+    float rv[R], kv[R];
+    piece(a.r + t * a.r_ts, rv, a.silu != 0);
+    piece(a.k + t * a.k_ts, kv, a.silu != 0);
+    float vj = col_on ? a.v[t * a.v_ts + h * dv + j] : 0.f;
+    if (a.silu) vj = vj / (1.f + expf(-vj));
+    if (MODE == AF_SCAN_DELTA) {
+      float wv[R], uv[R], av[R];
+      piece(a.w + t * a.w_ts, wv, false);
+      piece(a.u + t * a.u_ts, uv, false);
+      piece(a.au + t * a.au_ts, av, false);
+      float dot = 0.f;
+#pragma unroll
+      for (int i = 0; i < R; ++i) dot += uv[i] * S[i];
+      for (int o = 1; o < P; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+#pragma unroll
+      for (int i = 0; i < R; ++i) S[i] = wv[i] * S[i] - av[i] * dot + kv[i] * vj;
+    } else {
+#pragma unroll
+      for (int i = 0; i < R; ++i) S[i] = dec * S[i] + kv[i] * vj;
+    }
+    float o = 0.f;
+#pragma unroll
+    for (int i = 0; i < R; ++i) o += rv[i] * S[i];
+    for (int sft = 1; sft < P; sft <<= 1) o += __shfl_xor_sync(0xffffffffu, o, sft);
+    if (part == 0 && col_on) a.out[t * a.out_ts + h * dv + j] = o;
+    keep_state();
+    return;
+  }
+  for (int i = tid; i < 2 * buf_floats; i += nthr) smem[i] = 0.f;        // (the padding stays zero for good)
+
+  // The loads of a chunk are all issued before any of their values is used (what is done to a value, the
+  // activation, is done when it is staged).  Which tokens and channels a thread fetches does not change from
+  // chunk to chunk: the places are worked out once.
+  constexpr int FE = VEC ? AF_SCAN_VEC_ITEMS : AF_SCAN_PREFETCH;   // key-vector items a thread fetches (per vector if VEC)
+  constexpr int FV = VEC ? AF_SCAN_VEC_ITEMS : 1;                  // value-tile items
+  float4 pq[VEC ? 5 : 1][VEC ? FE : 1], pvq[FV];
+  float pf[VEC ? 1 : AF_SCAN_PREFETCH];
+  int ftt[VEC ? FE : 1], fgo[VEC ? FE : 1], fso[VEC ? FE : 1], vtt[FV], vgo[FV], vso[FV];
+  if constexpr (VEC) {
+    const int dkq = dk >> 2, ctq = CT >> 2;
+#pragma unroll
+    for (int e = 0; e < FE; ++e) {
       const int idx = tid + e * nthr;
-      float val = 0.f;
-      if (idx < n * tok_vals) {
-        const int tt = idx / tok_vals, x = idx - tt * tok_vals;
-        const size_t t = (size_t)(t0 + tt);
-        if (x < NV * dk) {
-          const int vec = x / dk, c = x - vec * dk;
-          const float* p = vec == 0 ? a.r + t * a.r_ts : vec == 1 ? a.k + t * a.k_ts
-                         : vec == 2 ? a.w + t * a.w_ts : vec == 3 ? a.u + t * a.u_ts : a.au + t * a.au_ts;
-          val = p[h * dk + c];
-          if (a.silu) val = val / (1.f + expf(-val));
-        } else {
-          const int jj = j0 + x - NV * dk;
-          if (jj < dv) {
-            val = a.v[t * a.v_ts + h * dv + jj];
-            if (a.silu) val = val / (1.f + expf(-val));
+      const int tt = idx / dkq, c = (idx - tt * dkq) * 4;
+      ftt[e] = idx < CH * dkq ? tt : CH;                     // (CH: never among a chunk's tokens)
+      fgo[e] = h * dk + c;
+      fso[e] = tt * tok_floats + (c / R) * (R + 4) + c % R;
+    }
+#pragma unroll
+    for (int e = 0; e < FV; ++e) {
+      const int idx = tid + e * nthr;
+      const int tt = idx / ctq, x = (idx - tt * ctq) * 4;
+      vtt[e] = (idx < CH * ctq && j0 + x < dv) ? tt : CH;
+      vgo[e] = h * dv + j0 + x;
+      vso[e] = tt * tok_floats + NV * dkp + x;
+    }
+  }
+  auto act4 = [&](float4 q) {
+    q.x = q.x / (1.f + expf(-q.x)), q.y = q.y / (1.f + expf(-q.y));
+    q.z = q.z / (1.f + expf(-q.z)), q.w = q.w / (1.f + expf(-q.w));
+    return q;
+  };
+  auto fetch = [&](int t0, int n) {                          // tokens t0 .. t0 + n - 1 into registers
+    if constexpr (VEC) {
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        const float* p = v == 0 ? a.r : v == 1 ? a.k : v == 2 ? a.w : v == 3 ? a.u : a.au;
+        const long long ts = v == 0 ? a.r_ts : v == 1 ? a.k_ts : v == 2 ? a.w_ts : v == 3 ? a.u_ts : a.au_ts;
+#pragma unroll
+        for (int e = 0; e < FE; ++e)
+          if (ftt[e] < n) pq[v][e] = *reinterpret_cast<const float4*>(p + (size_t)(t0 + ftt[e]) * ts + fgo[e]);
+      }
+#pragma unroll
+      for (int e = 0; e < FV; ++e)
+        if (vtt[e] < n) pvq[e] = *reinterpret_cast<const float4*>(a.v + (size_t)(t0 + vtt[e]) * a.v_ts + vgo[e]);
+    } else {
+#pragma unroll
+      for (int e = 0; e < AF_SCAN_PREFETCH; ++e) {
+        const int idx = tid + e * nthr;
+        float val = 0.f;
+        if (idx < n * tok_vals) {
+          const int tt = idx / tok_vals, x = idx - tt * tok_vals;
+          const size_t t = (size_t)(t0 + tt);
+          if (x < NV * dk) {
+            const int vec = x / dk, c = x - vec * dk;
+            const float* p = vec == 0 ? a.r + t * a.r_ts : vec == 1 ? a.k + t * a.k_ts
+                           : vec == 2 ? a.w + t * a.w_ts : vec == 3 ? a.u + t * a.u_ts : a.au + t * a.au_ts;
+            val = p[h * dk + c];
+          } else {
+            const int jj = j0 + x - NV * dk;
+            if (jj < dv) val = a.v[t * a.v_ts + h * dv + jj];
           }
         }
+        pf[e] = val;
       }
-      pf[e] = val;
     }
   };
   auto stage = [&](float* buf, int n) {                      // registers into a shared-memory buffer
+    if constexpr (VEC) {
 #pragma unroll
-    for (int e = 0; e < AF_SCAN_PREFETCH; ++e) {
-      const int idx = tid + e * nthr;
-      if (idx < n * tok_vals) {
-        const int tt = idx / tok_vals, x = idx - tt * tok_vals;
-        int at;
-        if (x < NV * dk) {
-          const int vec = x / dk, c = x - vec * dk;
-          at = vec * dkp + (c / R) * (R + 4) + c % R;
-        } else {
-          at = NV * dkp + x - NV * dk;
+      for (int v = 0; v < NV; ++v)
+#pragma unroll
+        for (int e = 0; e < FE; ++e)
+          if (ftt[e] < n)
+            *reinterpret_cast<float4*>(buf + fso[e] + v * dkp) = (a.silu && v < 2) ? act4(pq[v][e]) : pq[v][e];
+#pragma unroll
+      for (int e = 0; e < FV; ++e)
+        if (vtt[e] < n) *reinterpret_cast<float4*>(buf + vso[e]) = a.silu ? act4(pvq[e]) : pvq[e];
+    } else {
+#pragma unroll
+      for (int e = 0; e < AF_SCAN_PREFETCH; ++e) {
+        const int idx = tid + e * nthr;
+        if (idx < n * tok_vals) {
+          const int tt = idx / tok_vals, x = idx - tt * tok_vals;
+          int at;
+          bool act = a.silu != 0;
+          if (x < NV * dk) {
+            const int vec = x / dk, c = x - vec * dk;
+            at = vec * dkp + (c / R) * (R + 4) + c % R;
+            act = act && vec < 2;
+          } else {
+            at = NV * dkp + x - NV * dk;
+          }
+          buf[tt * tok_floats + at] = act ? pf[e] / (1.f + expf(-pf[e])) : pf[e];
         }
-        buf[tt * tok_floats + at] = pf[e];
       }
     }
   };
@@ -184,6 +316,7 @@ state_scan_kernel(AfScanArgs a) {
     const int t1 = t0 + n;
     const int n1 = min(CH, last - t1);
     if (n1 > 0) fetch(t1, n1);                               // under the scan of this chunk
+#pragma unroll 2
     for (int tt = 0; tt < n; ++tt) {
       const float* tk = buf + tt * tok_floats + part * (R + 4);
       const float vj = buf[tt * tok_floats + NV * dkp + col];
@@ -229,18 +362,14 @@ state_scan_kernel(AfScanArgs a) {
     n = n1;
     which ^= 1;
   }
-  if (col_on) {
-#pragma unroll
-    for (int i = 0; i < R; ++i)
-      if (part * R + i < dk) st[i] = S[i];
-  }
+  keep_state();
 }
 
-template <int R>
+template <int R, bool VEC>
 static int launch_scan(const AfScanArgs& a, int mode, dim3 grid, int threads, size_t smem, cudaStream_t stream) {
   static bool raised[2][AF_MAX_DEVICES];
-  auto k0 = state_scan_kernel<R, AF_SCAN_DECAY>;
-  auto k1 = state_scan_kernel<R, AF_SCAN_DELTA>;
+  auto k0 = state_scan_kernel<R, AF_SCAN_DECAY, VEC>;
+  auto k1 = state_scan_kernel<R, AF_SCAN_DELTA, VEC>;
   if (smem > 48 * 1024) {
     const int dev = af_current_device();
     if (dev < 0) return -1;
@@ -256,17 +385,27 @@ static int launch_scan(const AfScanArgs& a, int mode, dim3 grid, int threads, si
 }
 
 // The cut of a scan: R key channels a lane, P lanes a column, CT columns a block, CH tokens a chunk.
-static void scan_cut(int mode, int dk, int dv, int* R, int* P, int* CT, int* CH) {
+// `vec`: the vectors are fetched in 16-byte pieces.  `want_blocks`: blocks that fill the device; while the grid
+// has fewer, the blocks take fewer columns each.
+static void scan_cut(int mode, int dk, int dv, bool vec, long long units, int want_blocks, int* R, int* P, int* CT,
+                     int* CH) {
   int r = 4;
   while (r < 32 && (dk + r - 1) / r > 8) r *= 2;            // up to eight lanes a column while a lane holds up to 32
   int p = 1;
   while (p * r < dk && p < 32) p *= 2;
   int ct = 128 / p;                                          // 128 threads a block
   while (ct > 4 && ct / 2 >= dv && (ct / 2) * p >= 32) ct /= 2;   // (no wider than the state's columns need; whole warps)
+  while (ct > 4 && (ct / 2) * p >= 64 && units * ((dv + ct - 1) / ct) < want_blocks) ct /= 2;
   const int nv = mode == AF_SCAN_DELTA ? 5 : 2;
   const int tok_vals = nv * dk + ct, tok_floats = nv * p * (r + 4) + ct;
+  const int threads = ct * p;
   int ch = 16;
-  while (ch > 1 && (ch * tok_vals > AF_SCAN_PREFETCH * ct * p || 2 * ch * tok_floats * 4 > 96 * 1024)) ch /= 2;
+  while (ch > 1 && 2 * ch * tok_floats * 4 > 96 * 1024) ch /= 2;
+  if (vec) {
+    while (ch > 1 && (ch * (dk / 4) > AF_SCAN_VEC_ITEMS * threads || ch * (ct / 4) > AF_SCAN_VEC_ITEMS * threads)) ch /= 2;
+  } else {
+    while (ch > 1 && ch * tok_vals > AF_SCAN_PREFETCH * threads) ch /= 2;
+  }
   *R = r, *P = p, *CT = ct, *CH = ch;
 }
 
@@ -284,20 +423,40 @@ AF_EXPORT int af_state_scan(int mode, const float* r, long long r_ts, const floa
   a.r_ts = r_ts, a.k_ts = k_ts, a.v_ts = v_ts, a.w_ts = w_ts, a.u_ts = u_ts, a.au_ts = au_ts;
   a.decay = decay, a.state = state, a.out = out, a.out_ts = out_ts, a.seq_starts = seq_starts, a.slots = slots;
   a.heads = heads, a.dk = dk, a.dv = dv, a.silu = silu;
+  // whole 16-byte pieces: sizes and strides in multiples of four floats, bases on 16 bytes
+  bool vec = dk % 4 == 0 && dv % 4 == 0 && ((r_ts | k_ts | v_ts) & 3) == 0 &&
+             (((uintptr_t)r | (uintptr_t)k | (uintptr_t)v) & 15) == 0;
+  if (mode == AF_SCAN_DELTA)
+    vec = vec && ((w_ts | u_ts | au_ts) & 3) == 0 && (((uintptr_t)w | (uintptr_t)u | (uintptr_t)au) & 15) == 0;
+  const int sms = af_sm_count();
+  if (sms <= 0) return -1;
   int R, P, CT, CH;
-  scan_cut(mode, dk, dv, &R, &P, &CT, &CH);
+  scan_cut(mode, dk, dv, vec, (long long)heads * n_seqs, sms, &R, &P, &CT, &CH);
   AF_REQUIRE(P * R >= dk, "af_state_scan: key size %d does not fit %d lanes of %d", dk, P, R);
   const int nv = mode == AF_SCAN_DELTA ? 5 : 2;
-  AF_REQUIRE(CH * (nv * dk + CT) <= AF_SCAN_PREFETCH * CT * P, "af_state_scan: a token of %d values is too long to stage",
-             nv * dk + CT);
+  if (vec)
+    AF_REQUIRE(CH * (dk / 4) <= AF_SCAN_VEC_ITEMS * CT * P && CH * (CT / 4) <= AF_SCAN_VEC_ITEMS * CT * P,
+               "af_state_scan: a token of %d values is too long to stage", nv * dk + CT);
+  else
+    AF_REQUIRE(CH * (nv * dk + CT) <= AF_SCAN_PREFETCH * CT * P, "af_state_scan: a token of %d values is too long to stage",
+               nv * dk + CT);
   a.lanes = P, a.cols = CT, a.chunk = CH;
   const size_t smem = (size_t)2 * CH * (nv * P * (R + 4) + CT) * sizeof(float);
   const dim3 grid((dv + CT - 1) / CT, heads, n_seqs);
+  const int threads = CT * P;
+  if (vec) {
+    switch (R) {
+      case 4: return launch_scan<4, true>(a, mode, grid, threads, smem, stream);
+      case 8: return launch_scan<8, true>(a, mode, grid, threads, smem, stream);
+      case 16: return launch_scan<16, true>(a, mode, grid, threads, smem, stream);
+      default: return launch_scan<32, true>(a, mode, grid, threads, smem, stream);
+    }
+  }
   switch (R) {
-    case 4: return launch_scan<4>(a, mode, grid, CT * P, smem, stream);
-    case 8: return launch_scan<8>(a, mode, grid, CT * P, smem, stream);
-    case 16: return launch_scan<16>(a, mode, grid, CT * P, smem, stream);
-    default: return launch_scan<32>(a, mode, grid, CT * P, smem, stream);
+    case 4: return launch_scan<4, false>(a, mode, grid, threads, smem, stream);
+    case 8: return launch_scan<8, false>(a, mode, grid, threads, smem, stream);
+    case 16: return launch_scan<16, false>(a, mode, grid, threads, smem, stream);
+    default: return launch_scan<32, false>(a, mode, grid, threads, smem, stream);
   }
 }
 
@@ -351,47 +510,78 @@ AF_EXPORT int af_gated_group_norm(void* y, int y_dtype, const float* o, const fl
 
 // Per channel: z = sigmoid(pz + bz), c = px + bx, candidate = c + 1/2 where c >= 0 and sigmoid(c) below,
 // S <- (1 - z) S + z candidate, y = S * silu(pg).  pz, px, pg are sections of the packed projection row.
-// One thread per (sequence, channel); the loads of four tokens are issued before the chain goes on.
+// A block owns 32 channels of a sequence (a lane each) and walks its tokens 128 at a time: warp w takes 16
+// tokens in a row, works out what they do to any state that enters them (S_out = A S_in + B: the map of a
+// token is affine, and so is their composition), the warps exchange these pairs, each warp composes the pairs
+// of the warps before it onto the state carried so far, and then walks its 16 tokens once more from the state
+// that really enters them.  The gates and candidates of the 16 tokens stay in registers between the passes.
+#define AF_GS_WARPS 8
+#define AF_GS_RUN 16
 template <typename TY>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(AF_GS_WARPS * 32)
 gated_scan_kernel(TY* __restrict__ y, const float* __restrict__ proj, long long ld, int off_z, int off_x, int off_g,
                   const float* __restrict__ bz, const float* __restrict__ bx, float* __restrict__ state,
                   const int* __restrict__ seq_starts, const int* __restrict__ slots, int width) {
   pdl_launch_dependents();
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  __shared__ float comp[AF_GS_WARPS][32][2];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
   const int b = blockIdx.y;
-  if (c >= width) return;
+  const bool on = c < width;
   const int first = seq_starts[b], last = seq_starts[b + 1];
   const int slot = slots[b];
-  const float zb = bz[c], xb = bx[c];
+  const float zb = on ? bz[c] : 0.f, xb = on ? bx[c] : 0.f;
   pdl_wait();
   if (slot < 0) {
-    for (int t = first; t < last; ++t) y[(size_t)t * width + c] = from_f32<TY>(0.f);
+    if (on)
+      for (int t = first + w; t < last; t += AF_GS_WARPS) y[(size_t)t * width + c] = from_f32<TY>(0.f);
     return;
   }
-  float S = state[(size_t)slot * width + c];
-  for (int t = first; t < last; t += 4) {
-    float pz[4], px[4], pg[4];
+  float carry = on ? state[(size_t)slot * width + c] : 0.f;
+  for (int base = first; base < last; base += AF_GS_WARPS * AF_GS_RUN) {
+    const int t0 = base + w * AF_GS_RUN;
+    const int n = max(0, min(AF_GS_RUN, last - t0));
+    float z[AF_GS_RUN], cd[AF_GS_RUN], g[AF_GS_RUN];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const bool on = t + e < last;
-      const float* row = proj + (size_t)(t + e) * ld + c;
-      pz[e] = on ? row[off_z] : 0.f;
-      px[e] = on ? row[off_x] : 0.f;
-      pg[e] = on ? row[off_g] : 0.f;
+    for (int e = 0; e < AF_GS_RUN; ++e) {
+      const bool in = on && e < n;
+      const float* row = proj + (size_t)(t0 + e) * ld + c;
+      z[e] = in ? row[off_z] : 0.f;
+      cd[e] = in ? row[off_x] : 0.f;
+      g[e] = in ? row[off_g] : 0.f;
     }
+    float A = 1.f, B = 0.f;
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      if (t + e >= last) break;
-      const float z = 1.f / (1.f + expf(-(pz[e] + zb)));
-      const float u = px[e] + xb;
-      const float cand = u >= 0.f ? u + 0.5f : 1.f / (1.f + expf(-u));
-      S = (1.f - z) * S + z * cand;
-      const float g = pg[e];
-      y[(size_t)(t + e) * width + c] = from_f32<TY>(S * (g / (1.f + expf(-g))));
+    for (int e = 0; e < AF_GS_RUN; ++e) {
+      if (e < n) {
+        const float zz = 1.f / (1.f + expf(-(z[e] + zb)));
+        const float u = cd[e] + xb;
+        z[e] = zz;
+        cd[e] = u >= 0.f ? u + 0.5f : 1.f / (1.f + expf(-u));
+        A *= 1.f - zz;
+        B = (1.f - zz) * B + zz * cd[e];
+      }
     }
+    comp[w][lane][0] = A;
+    comp[w][lane][1] = B;
+    __syncthreads();
+    // the state that enters this warp's tokens, and the one that leaves the stretch (the same in every warp)
+    float S = carry, full = carry;
+    for (int v = 0; v < AF_GS_WARPS; ++v) {
+      if (v == w) S = full;
+      full = comp[v][lane][0] * full + comp[v][lane][1];
+    }
+    carry = full;
+#pragma unroll
+    for (int e = 0; e < AF_GS_RUN; ++e) {
+      if (e < n) {
+        S = (1.f - z[e]) * S + z[e] * cd[e];
+        if (on) y[(size_t)(t0 + e) * width + c] = from_f32<TY>(S * (g[e] / (1.f + expf(-g[e]))));
+      }
+    }
+    __syncthreads();
   }
-  state[(size_t)slot * width + c] = S;
+  if (on && w == 0) state[(size_t)slot * width + c] = carry;
 }
 
 AF_EXPORT int af_gated_scan(void* y, int y_dtype, const float* proj, long long ld, int off_z, int off_x, int off_g,
@@ -399,7 +589,7 @@ AF_EXPORT int af_gated_scan(void* y, int y_dtype, const float* proj, long long l
                             int n_seqs, int width, cudaStream_t stream) {
   if (n_seqs == 0) return 0;
   AF_REQUIRE(n_seqs > 0 && n_seqs < 65536 && width > 0, "af_gated_scan: bad sizes");
-  AF_DISPATCH_DTYPE(y_dtype, TY, af_launch(gated_scan_kernel<TY>, dim3((width + 127) / 128, n_seqs), dim3(128), 0, stream,
+  AF_DISPATCH_DTYPE(y_dtype, TY, af_launch(gated_scan_kernel<TY>, dim3((width + 31) / 32, n_seqs), dim3(AF_GS_WARPS * 32), 0, stream,
                                            (TY*)y, proj, ld, off_z, off_x, off_g, bz, bx, state, seq_starts, slots, width));
   AF_CHECK_LAUNCH("af_gated_scan");
 }

@@ -702,25 +702,25 @@ def _f32_rows(t, name):
     return _ptr(t, name), c_longlong(t.stride(0))
 
 
-def delta_prep(out, proj, off_k: int, off_a: int, off_w1: int, a_bias, w0, w2, heads: int, dk: int,
+def delta_prep(out, proj, off_k: int, off_a: int, off_w1: int, a_bias, w0, w2t, heads: int, dk: int,
                decay_scale: float, key_eps: float) -> None:
     """What enters the generalized delta rule besides r, k and v, from the packed float32 projection rows
     ``proj`` (sections at the given column offsets): out [T, 3, heads * dk] float32 = the decay
     exp(-decay_scale * sigmoid(w2 tanh(w1 section) + w0)), the unit key k / sqrt(sum k^2 + key_eps) per head,
-    and sigmoid(a section + a_bias) times the unit key."""
+    and sigmoid(a section + a_bias) times the unit key.  ``w2t`` is w2 transposed: [rank, heads * dk]."""
     T = proj.shape[0]
     n = heads * dk
-    rank = w2.shape[1]
+    rank = w2t.shape[0]
     if tuple(out.shape) != (T, 3, n) or out.dtype != torch.float32 or not out.is_contiguous():
         raise KernelError(f"delta_prep: out must be contiguous float32 [{T}, 3, {n}]")
-    if tuple(w2.shape) != (n, rank) or not w2.is_contiguous() or a_bias.numel() != n or w0.numel() != n:
-        raise KernelError("delta_prep: w2 [heads * dk, rank], a_bias and w0 [heads * dk]")
+    if tuple(w2t.shape) != (rank, n) or not w2t.is_contiguous() or a_bias.numel() != n or w0.numel() != n:
+        raise KernelError("delta_prep: w2t [rank, heads * dk], a_bias and w0 [heads * dk]")
     if max(off_k, off_a) + n > proj.shape[1] or off_w1 + rank > proj.shape[1]:
         raise KernelError("delta_prep: a section lies outside the projection row")
     pp, ld = _f32_rows(proj, "proj")
     _check(_lib().af_delta_prep(_ptr(out), pp, ld, c_int(off_k), c_int(off_a), c_int(off_w1),
                                 _ptr(a_bias, "a_bias", torch.float32), _ptr(w0, "w0", torch.float32),
-                                _ptr(w2, "w2", torch.float32), c_int(rank), c_int(T), c_int(heads), c_int(dk),
+                                _ptr(w2t, "w2t", torch.float32), c_int(rank), c_int(T), c_int(heads), c_int(dk),
                                 c_float(decay_scale), c_float(key_eps), _stream()))
 
 

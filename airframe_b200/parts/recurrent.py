@@ -109,12 +109,12 @@ class GeneralDelta(_StateMixer):
         f32 = torch.float32
         self.a_bias = weights[nm["a_bias"]].to(f32).contiguous()
         self.w0 = weights[nm["w0"]].to(f32).contiguous()
-        self.w2 = weights[nm["w2"]].to(f32).contiguous()
+        self.w2t = weights[nm["w2"]].to(f32).t().contiguous()      # [rank, heads * dim]: channels side by side
         self.norm_w = weights[nm["norm"]].to(f32).contiguous()
         self.w_o = weights[nm["o"]].to(self.ctx.compute_dtype).contiguous()
 
     def decode_bytes(self, lens) -> int:
-        weights = (self.w_in.numel() + self.w_o.numel()) * _el(self.ctx) + 4 * self.w2.numel()
+        weights = (self.w_in.numel() + self.w_o.numel()) * _el(self.ctx) + 4 * self.w2t.numel()
         return weights + len(lens) * 2 * 4 * self.heads * self.hd * self.hd      # the state, read and written
 
     def prefill_flops(self, lens) -> int:
@@ -125,7 +125,7 @@ class GeneralDelta(_StateMixer):
         T, n, off = x.shape[0], self.n, self.off
         proj = linear(x, self.w_in, out_dtype=torch.float32)
         pre = torch.empty(T, 3, n, dtype=torch.float32, device=x.device)
-        kernels.delta_prep(pre, proj, off["k"], off["a"], off["w1"], self.a_bias, self.w0, self.w2, self.heads,
+        kernels.delta_prep(pre, proj, off["k"], off["a"], off["w1"], self.a_bias, self.w0, self.w2t, self.heads,
                            self.hd, self.decay_scale, self.key_eps)
         o = torch.empty(T, n, dtype=torch.float32, device=x.device)
         kernels.state_scan("delta", o, proj[:, off["r"]: off["r"] + n], proj[:, off["k"]: off["k"] + n],

@@ -447,6 +447,130 @@ def attention_points() -> None:
     case("27b sizes, 16 of 1,024 ... 8,194", 32, 16, 128, [1024 + i * 478 for i in range(16)], 2)
 
 
+# ---------------------------------------------------------------- --fiferax: the state mixers beside attention
+
+def _fiferax_sizes(width, layers, heads, dim, kv_heads, attn_dim, window, ff, vocab):
+    """A Fiferax model of `layers` layers in the order delta rule, parallel (+ feed-forward), delta rule, gated
+    recurrence (+ feed-forward), and the Gemma-2 model of the same width, depth, feed-forward and vocabulary."""
+    decay = [1.0 - 2.0 ** (-5 - 4 * h / max(heads - 1, 1)) for h in range(heads)]
+    par = {"left": {"heads": width // attn_dim, "kv_heads": kv_heads, "dim": attn_dim, "vdim": attn_dim,
+                    "mask": {"size": window}, "rot": {"base": 10000.0, "dims": attn_dim}, "scale": attn_dim ** -0.5},
+           "left_scale": 1.0, "right": {"heads": heads, "dim": dim, "vdim": dim, "decay": decay}, "right_scale": 1.0}
+    order = [("general_delta", {"heads": heads, "dim": dim, "rank": 64}, None), ("parallel", par, ff),
+             ("general_delta", {"heads": heads, "dim": dim, "rank": 64}, None), ("mingru", {"width": width}, ff)]
+    fx = {"architecture": "Fiferax", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+          "layers": [{"type": t, "mixer": m, "mlp": None if f is None else {"kind": "dense", "ff": f}}
+                     for t, m, f in (order[i % 4] for i in range(layers))]}
+    gemma = dict(GEMMA2_2B, num_hidden_layers=layers, hidden_size=width, num_attention_heads=width // attn_dim,
+                 num_key_value_heads=kv_heads, head_dim=attn_dim, intermediate_size=ff, vocab_size=vocab,
+                 sliding_window=window, query_pre_attn_scalar=attn_dim)
+    return fx, gemma
+
+
+FIFERAX_POINTS = {
+    "w1024": dict(width=1024, layers=8, heads=16, dim=64, kv_heads=4, attn_dim=64, window=1024, ff=4096, vocab=32000),
+    "w2304": dict(width=2304, layers=8, heads=18, dim=128, kv_heads=3, attn_dim=256, window=4096, ff=9216, vocab=32000),
+    "w4096": dict(width=4096, layers=8, heads=32, dim=128, kv_heads=8, attn_dim=128, window=4096, ff=14336, vocab=32000),
+}
+
+
+def fiferax_points(args) -> None:
+    """Prefill (one prompt of 2,048 tokens) and decode (batch 8 after such prompts, the captured step, logits
+    out) of Fiferax at a few layer sizes, each beside the Gemma-2 model of equal width, depth, feed-forward and
+    vocabulary; and where a step's time goes, kernel by kernel.  One JSON line a model."""
+    import torch
+    sys.path.insert(0, str(ROOT))
+    from torch.profiler import ProfilerActivity, profile
+    from airframe_b200.config import config_from_dict
+    from airframe_b200.engine import GpuRuntime, StepEntry
+
+    pk = peaks()
+    B, P, K, W = args.batch or 8, args.prompt_len or 2048, args.steps or 64, max(args.warmup, 3)
+
+    def timed(fn, n):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(n):
+            fn()
+        end.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(end) / n
+
+    def kernels_of(fn):
+        """Device time of every kernel of one call, summed by kernel name (under the CUDA profiler of PyTorch;
+        a kernel is charged from the end of what ran before it to its own end)."""
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            fn()
+            torch.cuda.synchronize()
+        evs = sorted((e for e in prof.events() if "cuda" in str(e.device_type).lower()), key=lambda e: e.time_range.start)
+        out, busy = {}, None
+        for e in evs:
+            start, end = e.time_range.start, e.time_range.end
+            own = end - start if busy is None else max(0.0, end - max(start, busy))
+            busy = end if busy is None else max(busy, end)
+            name = e.name.replace("void ", "").split("<")[0].split("(")[0][:48]
+            if "<" in e.name:                                  # (template arguments tell variants apart; types shortened)
+                name += "<" + e.name.split("<", 1)[1].split(">(")[0].replace("__nv_bfloat16", "bf16").replace("(int)", "")
+                name = name.replace("(AfEpilogue)", "").replace("(bool)", "")[:72] + ">"
+            n, us = out.get(name, (0, 0.0))
+            out[name] = (n + 1, us + own)
+        return {k: {"n": n, "us": round(us, 1)} for k, (n, us) in sorted(out.items(), key=lambda kv: -kv[1][1])}
+
+    for tag, sizes in FIFERAX_POINTS.items():
+        if args.fiferax not in ("all", tag):
+            continue
+        for arm, cfg_dict in zip(("fiferax", "gemma2"), _fiferax_sizes(**sizes)):
+            cfg = config_from_dict(cfg_dict)
+            V = cfg_dict.get("vocab") or cfg_dict["vocab_size"]
+            budget = B * ((P + K + W + 8 + 63) // 64 * 64)
+            rt = GpuRuntime.random(cfg, seed=0, dtype="bfloat16", max_tokens=budget, max_context=CONTEXT,
+                                   max_sequences=B, on_device=True)
+            eng, model = rt.engine, rt.engine.model
+            g = torch.Generator().manual_seed(1)
+            ps = [torch.randint(0, V, (P,), generator=g).tolist() for _ in range(B)]
+
+            def prefill_once():
+                s = eng.take_slot()
+                try:
+                    eng.step([StepEntry(s, ps[0], [P - 1])])
+                finally:
+                    eng.free_slot(s)
+
+            for _ in range(3):
+                prefill_once()
+            pf_ms = timed(prefill_once, 5)
+            pf_kernels = kernels_of(prefill_once)
+            slots = [eng.take_slot() for _ in range(B)]
+            eng.step([StepEntry(s, p, [P - 1]) for s, p in zip(slots, ps)])
+            tok = [1] * B
+
+            def one():
+                eng.step([StepEntry(s, [t], [0]) for s, t in zip(slots, tok)], borrow=True)
+
+            one()
+            eng.repeat_last_decode(SETTLE)
+            for _ in range(W):
+                one()
+            ms = timed(one, K)
+            dec_kernels = kernels_of(one)
+            lens = [eng.length(s) for s in slots]
+            need = model.decode_bytes(lens)
+            flops = model.prefill_flops([P], 1)
+            print(json.dumps({
+                "point": tag, "model": arm, "sizes": sizes, "batch": B, "prompt": P, "steps": K, "warmup": W,
+                "prefill": {"tokens_per_s": P / (pf_ms / 1e3), "ms": pf_ms, "flops": flops,
+                            "frac_of_bf16_peak": flops / (pf_ms / 1e3) / (pk["bf16_tflops"] * 1e12), "kernels": pf_kernels},
+                "decode": {"tokens_per_s": B / (ms / 1e3), "ms_per_step": ms, "bytes": need,
+                           "frac_of_hbm_roofline": need / (ms / 1e3) / 1e9 / pk["hbm_gbs"], "kernels": dec_kernels},
+                "peaks": pk["source"], "dtype": "bf16", "data": "synthetic: seeded random weights and token ids"}),
+                flush=True)
+            for s in slots:
+                eng.free_slot(s)
+            del rt, eng, model
+            torch.cuda.empty_cache()
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -466,6 +590,9 @@ def main() -> int:
                     help="time the decode attention kernels alone at the workloads' shapes, then exit")
     ap.add_argument("--sizes", default="2b", choices=sorted(SIZES),
                     help="layer sizes of this Gemma-2 model, with the workload named for them")
+    ap.add_argument("--fiferax", default="", choices=["", "all", *sorted(FIFERAX_POINTS)],
+                    help="prefill and decode of Fiferax at layer sizes like a real model's, beside Gemma-2 of equal "
+                         "size, then exit (not the default run)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -477,6 +604,9 @@ def main() -> int:
         return 2
     if args.attention:
         attention_points()
+        return 0
+    if args.fiferax:
+        fiferax_points(args)
         return 0
     line = run_ours(args)
     if line is not None:
