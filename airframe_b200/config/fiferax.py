@@ -129,7 +129,7 @@ class FiferaxConfig(ModelConfig):
             "scale": float(left["scale"]), "softcap": 0.0, "window": left["mask"]["size"],
             "position": PartSpec("rope", {"theta": float(left["rot"]["base"]), "rotary_dim": left["rot"]["dims"],
                                           "pairing": "half"}),
-            "q_weight": lp + "q", "k_weight": lp + "k", "v_weight": None, "o_weight": lp + "o",
+            "q_weight": lp + "q", "k_weight": lp + "k", "v_weight": None, "o_weight": lp + "o", "wide_output": True,
             "qk_norm": {"q_weight": lp + "q.norm", "k_weight": lp + "k.norm", "eps": eps}})
         lightning = PartSpec("lightning_attention", {
             "hidden_size": h, "num_heads": right["heads"], "head_dim": right["dim"], "value_dim": right["vdim"],
@@ -152,7 +152,8 @@ class FiferaxConfig(ModelConfig):
                 ffn = PartSpec("none")
             else:
                 ffn = PartSpec("gated_mlp", {"hidden_size": h, "intermediate_size": layer["mlp"]["ff"],
-                                             "activation": "gelu_tanh", "gate_weight": p + "mlp.gate",
+                                             "activation": "gelu_tanh", "wide_output": True,
+                                             "gate_weight": p + "mlp.gate",
                                              "up_weight": p + "mlp.up", "down_weight": p + "mlp.down"})
                 norms["pre_feed_forward"] = norm(p + "norm2")
             layers.append(LayerSpec(prefix=p, block=PartSpec("prenorm"),

@@ -164,45 +164,6 @@ state_scan_kernel(AfScanArgs a) {
     }
   };
 
-  if (last - first == 1) {
-    // One token (a decode step): its vectors go from memory to the lanes' registers, nothing is staged.
-    const size_t t = (size_t)first;
-    const int c0 = part * R;
-    auto piece = [&](const float* p, float* dst, bool act) {
-#pragma unroll
-      for (int i = 0; i < R; ++i) {
-        float x = c0 + i < dk ? p[h * dk + c0 + i] : 0.f;
-        dst[i] = act ? x / (1.f + expf(-x)) : x;
-      }
-    };
-    float rv[R], kv[R];
-    piece(a.r + t * a.r_ts, rv, a.silu != 0);
-    piece(a.k + t * a.k_ts, kv, a.silu != 0);
-    float vj = col_on ? a.v[t * a.v_ts + h * dv + j] : 0.f;
-    if (a.silu) vj = vj / (1.f + expf(-vj));
-    if (MODE == AF_SCAN_DELTA) {
-      float wv[R], uv[R], av[R];
-      piece(a.w + t * a.w_ts, wv, false);
-      piece(a.u + t * a.u_ts, uv, false);
-      piece(a.au + t * a.au_ts, av, false);
-      float dot = 0.f;
-#pragma unroll
-      for (int i = 0; i < R; ++i) dot += uv[i] * S[i];
-      for (int o = 1; o < P; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-#pragma unroll
-      for (int i = 0; i < R; ++i) S[i] = wv[i] * S[i] - av[i] * dot + kv[i] * vj;
-    } else {
-#pragma unroll
-      for (int i = 0; i < R; ++i) S[i] = dec * S[i] + kv[i] * vj;
-    }
-    float o = 0.f;
-#pragma unroll
-    for (int i = 0; i < R; ++i) o += rv[i] * S[i];
-    for (int sft = 1; sft < P; sft <<= 1) o += __shfl_xor_sync(0xffffffffu, o, sft);
-    if (part == 0 && col_on) a.out[t * a.out_ts + h * dv + j] = o;
-    keep_state();
-    return;
-  }
   for (int i = tid; i < 2 * buf_floats; i += nthr) smem[i] = 0.f;        // (the padding stays zero for good)
 
   // The loads of a chunk are all issued before any of their values is used (what is done to a value, the
@@ -365,6 +326,107 @@ state_scan_kernel(AfScanArgs a) {
   keep_state();
 }
 
+// A step in which every sequence brings one token (a decode step): one block per (column tile, head,
+// sequence) as above, but nothing is staged: the token's vectors go from memory to the lanes' registers, the
+// state's tile is read, updated and written back.  `vec`: whole 16-byte pieces.
+template <int R, int MODE>
+__global__ void __launch_bounds__(128)
+state_step_kernel(AfScanArgs a, int vec) {
+  pdl_launch_dependents();
+  const int P = a.lanes, CT = a.cols, dk = a.dk, dv = a.dv;
+  const int tid = threadIdx.x;
+  const int part = tid % P, col = tid / P;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int j = blockIdx.x * CT + col;
+  const bool col_on = j < dv;
+  const int slot = a.slots[b];
+  const size_t t = (size_t)a.seq_starts[b];
+  const int c0 = part * R;
+  if (slot < 0) {
+    pdl_wait();
+    if (part == 0 && col_on) a.out[t * a.out_ts + h * dv + j] = 0.f;
+    return;
+  }
+  // the state is what the step before left: it does not wait for the kernel in front
+  float S[R];
+  float* st = a.state + (((size_t)slot * a.heads + h) * dv + (col_on ? j : 0)) * dk + c0;
+  if (vec) {
+#pragma unroll
+    for (int i = 0; i < R; i += 4) {
+      float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (col_on && c0 + i < dk) q = *reinterpret_cast<const float4*>(st + i);
+      S[i] = q.x, S[i + 1] = q.y, S[i + 2] = q.z, S[i + 3] = q.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < R; ++i) S[i] = (col_on && c0 + i < dk) ? st[i] : 0.f;
+  }
+  const float dec = MODE == AF_SCAN_DECAY ? a.decay[h] : 0.f;
+  pdl_wait();
+  auto piece = [&](const float* p, float* dst, bool act) {
+    p += h * dk + c0;
+    if (vec) {
+#pragma unroll
+      for (int i = 0; i < R; i += 4) {
+        float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c0 + i < dk) q = *reinterpret_cast<const float4*>(p + i);
+        dst[i] = q.x, dst[i + 1] = q.y, dst[i + 2] = q.z, dst[i + 3] = q.w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < R; ++i) dst[i] = c0 + i < dk ? p[i] : 0.f;
+    }
+    if (act) {
+#pragma unroll
+      for (int i = 0; i < R; ++i) dst[i] = dst[i] / (1.f + expf(-dst[i]));
+    }
+  };
+  float rv[R], kv[R];
+  piece(a.r + t * a.r_ts, rv, a.silu != 0);
+  piece(a.k + t * a.k_ts, kv, a.silu != 0);
+  float vj = col_on ? a.v[t * a.v_ts + h * dv + j] : 0.f;
+  if (a.silu) vj = vj / (1.f + expf(-vj));
+  if (MODE == AF_SCAN_DELTA) {
+    float wv[R], uv[R], av[R];
+    piece(a.w + t * a.w_ts, wv, false);
+    piece(a.u + t * a.u_ts, uv, false);
+    piece(a.au + t * a.au_ts, av, false);
+    float d0 = 0.f, d1 = 0.f;
+#pragma unroll
+    for (int i = 0; i < R; i += 2) d0 += uv[i] * S[i], d1 += uv[i + 1] * S[i + 1];
+    float dot = d0 + d1;
+    for (int o = 1; o < P; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+#pragma unroll
+    for (int i = 0; i < R; ++i) S[i] = wv[i] * S[i] - av[i] * dot + kv[i] * vj;
+  } else {
+#pragma unroll
+    for (int i = 0; i < R; ++i) S[i] = dec * S[i] + kv[i] * vj;
+  }
+  float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+  for (int i = 0; i < R; i += 2) o0 += rv[i] * S[i], o1 += rv[i + 1] * S[i + 1];
+  float o = o0 + o1;
+  for (int sft = 1; sft < P; sft <<= 1) o += __shfl_xor_sync(0xffffffffu, o, sft);
+  if (part == 0 && col_on) a.out[t * a.out_ts + h * dv + j] = o;
+  if (!col_on) return;
+  if (vec) {
+#pragma unroll
+    for (int i = 0; i < R; i += 4)
+      if (c0 + i < dk) *reinterpret_cast<float4*>(st + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < R; ++i)
+      if (c0 + i < dk) st[i] = S[i];
+  }
+}
+
+template <int R>
+static int launch_step(const AfScanArgs& a, int mode, int vec, dim3 grid, int threads, cudaStream_t stream) {
+  if (mode == AF_SCAN_DELTA) af_launch(state_step_kernel<R, AF_SCAN_DELTA>, grid, dim3(threads), 0, stream, a, vec);
+  else af_launch(state_step_kernel<R, AF_SCAN_DECAY>, grid, dim3(threads), 0, stream, a, vec);
+  AF_CHECK_LAUNCH("af_state_scan");
+}
+
 template <int R, bool VEC>
 static int launch_scan(const AfScanArgs& a, int mode, dim3 grid, int threads, size_t smem, cudaStream_t stream) {
   static bool raised[2][AF_MAX_DEVICES];
@@ -412,8 +474,8 @@ static void scan_cut(int mode, int dk, int dv, bool vec, long long units, int wa
 AF_EXPORT int af_state_scan(int mode, const float* r, long long r_ts, const float* k, long long k_ts, const float* v,
                             long long v_ts, const float* w, long long w_ts, const float* u, long long u_ts,
                             const float* au, long long au_ts, const float* decay, float* state, float* out,
-                            long long out_ts, const int* seq_starts, const int* slots, int n_seqs, int heads, int dk,
-                            int dv, int silu, cudaStream_t stream) {
+                            long long out_ts, const int* seq_starts, const int* slots, int n_seqs, int n_tokens, int heads,
+                            int dk, int dv, int silu, cudaStream_t stream) {
   if (n_seqs == 0) return 0;
   AF_REQUIRE(mode == AF_SCAN_DECAY || mode == AF_SCAN_DELTA, "af_state_scan: mode %d", mode);
   AF_REQUIRE(n_seqs > 0 && heads > 0 && dk > 0 && dv > 0 && dk <= 1024, "af_state_scan: bad sizes (key size up to 1024)");
@@ -441,6 +503,15 @@ AF_EXPORT int af_state_scan(int mode, const float* r, long long r_ts, const floa
     AF_REQUIRE(CH * (nv * dk + CT) <= AF_SCAN_PREFETCH * CT * P, "af_state_scan: a token of %d values is too long to stage",
                nv * dk + CT);
   a.lanes = P, a.cols = CT, a.chunk = CH;
+  if (n_tokens == n_seqs) {                                  // every sequence brings one token
+    const dim3 grid((dv + CT - 1) / CT, heads, n_seqs);
+    switch (R) {
+      case 4: return launch_step<4>(a, mode, vec ? 1 : 0, grid, CT * P, stream);
+      case 8: return launch_step<8>(a, mode, vec ? 1 : 0, grid, CT * P, stream);
+      case 16: return launch_step<16>(a, mode, vec ? 1 : 0, grid, CT * P, stream);
+      default: return launch_step<32>(a, mode, vec ? 1 : 0, grid, CT * P, stream);
+    }
+  }
   const size_t smem = (size_t)2 * CH * (nv * P * (R + 4) + CT) * sizeof(float);
   const dim3 grid((dv + CT - 1) / CT, heads, n_seqs);
   const int threads = CT * P;

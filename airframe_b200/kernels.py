@@ -733,7 +733,8 @@ def state_scan(mode: str, out, r, k, v, state, batch, heads: int, dk: int, dv: i
     ``delta``: S <- diag(w) S - au (u^T S) + k v^T, o = S^T r (both terms read the old S).
 
     r, k, w, u, au: float32 rows [T, heads * dk] (column sections allowed), v [T, heads * dv], out float32
-    [T, heads * dv].  ``silu``: r, k and v pass through x * sigmoid(x) as they are read."""
+    [T, heads * dv].  ``silu``: r, k and v pass through x * sigmoid(x) as they are read.  A step in which
+    every sequence brings one token (T == sequences) runs a kernel of its own that stages nothing."""
     if mode not in SCAN_MODES:
         raise KernelError(f"state_scan: unknown mode '{mode}'")
     T = out.shape[0]
@@ -757,7 +758,8 @@ def state_scan(mode: str, out, r, k, v, state, batch, heads: int, dk: int, dv: i
     _check(_lib().af_state_scan(c_int(SCAN_MODES[mode]), *rp, *kp, *vp, *extra[0], *extra[1], *extra[2], dec,
                                 _ptr(state, "state", torch.float32), *op,
                                 _ptr(batch.seq_starts, "seq_starts", torch.int32), _ptr(batch.slots, "slots", torch.int32),
-                                c_int(batch.n_seqs), c_int(heads), c_int(dk), c_int(dv), c_int(1 if silu else 0), _stream()))
+                                c_int(batch.n_seqs), c_int(T), c_int(heads), c_int(dk), c_int(dv), c_int(1 if silu else 0),
+                                _stream()))
 
 
 def gated_group_norm(y, o, w, gate, group: int, eps: float) -> None:

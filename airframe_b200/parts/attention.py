@@ -34,7 +34,8 @@ class Attention(Mixer):
     (a PartSpec of category ``position``), ``q_weight``/``k_weight``/``v_weight``/
     ``o_weight`` (tensor names; ``v_weight`` None or absent: the values are the keys as
     projected); optional ``qk_norm``: {``q_weight``, ``k_weight`` (tensor names of head_dim
-    values each), ``eps``}; optional ``rope_epilogue`` (default false): run the
+    values each), ``eps``}; optional ``wide_output`` (default false): the output projection's
+    result stays float32 on its way into the residual sum; optional ``rope_epilogue`` (default false): run the
     q, k, v projection with the rotary encoding and the cache write in its epilogue
     (``kernels.gemm_tc_rope``) where sizes and encoding allow.  Off by default
     because it measures slower than the projection followed by the rotary kernel:
@@ -211,4 +212,4 @@ class Attention(Mixer):
             kernels.attn_prefill(ctx, q, k, v, batch, nq, nkv, hd, self.scale, self.softcap, window, slopes)
         else:
             kernels.attn_decode(ctx, q, kv, batch, nq, nkv, hd, self.scale, self.softcap, window, slopes)
-        return linear_split(ctx, self.w_o)
+        return linear_split(ctx, self.w_o, wide=bool(self.params.get("wide_output", False)))

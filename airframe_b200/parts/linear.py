@@ -61,21 +61,25 @@ def as_terms(a) -> list:
     return [(a, 1.0)]
 
 
-def linear_split(x, w):
+def linear_split(x, w, wide: bool = False):
     """x w^T for few rows and a long K: split-K partial sums when that fills
-    the GPU better, else the plain result.  Returns a tensor or PartialSums."""
+    the GPU better, else the plain result.  Returns a tensor or PartialSums.
+    ``wide``: the plain result is float32 whatever the compute dtype (a
+    sublayer's output on its way into the 32-bit residual stream is then not
+    rounded to 16 bits in between)."""
     M, K = x.shape
     N = w.shape[0]
+    out_dtype = torch.float32 if wide else x.dtype
     if kernels.gemm_tc_supported(x, w, None):
         splits = kernels.gemm_tc_splits(M, N, K)
         if splits > 1:
             parts = torch.empty(splits, M, N, dtype=torch.float32, device=x.device)
             kernels.gemm_tc(parts, x, w, splits=splits, checked=True)
             return PartialSums(parts)
-        out = torch.empty(M, N, dtype=x.dtype, device=x.device)
+        out = torch.empty(M, N, dtype=out_dtype, device=x.device)
         kernels.gemm_tc(out, x, w, checked=True)
         return out
-    return linear(x, w)
+    return linear(x, w, out_dtype=out_dtype)
 
 
 def gated_linear(x, w_gu, inter: int, activation: str, interleaved: bool):

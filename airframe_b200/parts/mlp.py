@@ -18,7 +18,9 @@ from .linear import gated_linear, linear_split
 @register_part("feed_forward", "gated_mlp")
 class GatedMlp(FeedForward):
     """Parameters: ``hidden_size``, ``intermediate_size``, ``activation``
-    (``gelu_tanh`` or ``silu``), ``gate_weight``/``up_weight``/``down_weight``."""
+    (``gelu_tanh`` or ``silu``), ``gate_weight``/``up_weight``/``down_weight``; optional
+    ``wide_output`` (default false): the down projection's result stays float32 on its way
+    into the residual sum."""
     graph_safe = True
 
 
@@ -59,7 +61,7 @@ class GatedMlp(FeedForward):
 
     def forward(self, x, batch):
         h = gated_linear(x, self.w_gu, self.inter, self.activation, self.interleaved)
-        return linear_split(h, self.w_down)
+        return linear_split(h, self.w_down, wide=bool(self.params.get("wide_output", False)))
 
 
 @register_part("feed_forward", "none")

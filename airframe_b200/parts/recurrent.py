@@ -42,8 +42,14 @@ def _el(ctx) -> int:
 
 
 class _StateMixer(Mixer):
-    """What the three have in common: named tensors, one packed projection."""
+    """What the three have in common: named tensors, one packed projection, and an
+    output projection whose result goes to the residual sum in 32 bits (optional
+    parameter ``wide_output``, default true)."""
     graph_safe = True
+
+    @property
+    def wide(self) -> bool:
+        return bool(self.params.get("wide_output", True))
 
     def _names(self, roles):
         names = self.param("weights")
@@ -133,7 +139,7 @@ class GeneralDelta(_StateMixer):
                            w=pre[:, 0], u=pre[:, 1], au=pre[:, 2])
         y = torch.empty(T, n, dtype=x.dtype, device=x.device)
         kernels.gated_group_norm(y, o, self.norm_w, proj[:, off["g"]: off["g"] + n], self.hd, self.eps)
-        return linear_split(y, self.w_o)
+        return linear_split(y, self.w_o, wide=self.wide)
 
 
 @register_part("mixer", "lightning_attention")
@@ -189,7 +195,7 @@ class LightningAttention(_StateMixer):
                            decay=self.decay, silu=True)
         y = torch.empty(T, nv, dtype=x.dtype, device=x.device)
         kernels.gated_group_norm(y, o, self.norm_w, proj[:, off["g"]: off["g"] + nv], nv, self.eps)
-        return linear_split(y, self.w_o)
+        return linear_split(y, self.w_o, wide=self.wide)
 
 
 @register_part("mixer", "mingru")
@@ -230,4 +236,4 @@ class MinGru(_StateMixer):
         proj = linear(x, self.w_in, out_dtype=torch.float32)
         y = torch.empty(x.shape[0], self.width, dtype=x.dtype, device=x.device)
         kernels.gated_scan(y, proj, off["z"], off["x"], off["g"], self.z_bias, self.x_bias, view.state, batch)
-        return linear_split(y, self.w_o)
+        return linear_split(y, self.w_o, wide=self.wide)

@@ -509,7 +509,7 @@ def fiferax_points(args) -> None:
             start, end = e.time_range.start, e.time_range.end
             own = end - start if busy is None else max(0.0, end - max(start, busy))
             busy = end if busy is None else max(busy, end)
-            name = e.name.replace("void ", "").split("<")[0].split("(")[0][:48]
+            name = e.name.replace("void ", "").replace("(anonymous namespace)::", "").split("<")[0].split("(")[0][:48]
             if "<" in e.name:                                  # (template arguments tell variants apart; types shortened)
                 name += "<" + e.name.split("<", 1)[1].split(">(")[0].replace("__nv_bfloat16", "bf16").replace("(int)", "")
                 name = name.replace("(AfEpilogue)", "").replace("(bool)", "")[:72] + ">"
