@@ -36,7 +36,7 @@ def main(argv=None, stdin=None, stdout=None) -> int:
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time (each rounded up to 64)")
+                    help="most tokens live requests hold at any time")
     ap.add_argument("--device", default="cuda:0")
     ap.add_argument("--layers", action="store_true",
                     help="also write <step>.layers.json: per layer RMS, first values and checksum of the wanted rows")
@@ -52,10 +52,11 @@ def main(argv=None, stdin=None, stdout=None) -> int:
     out_dir = Path(args.out)
     out_dir.mkdir(parents=True, exist_ok=True)
     limit = config_from_folder(args.model).model_spec().max_positions
-    # the cache holds whole pages a sequence: up to a page less one token of slack for each of up to 64 live requests
-    slack = (kernels.PAGE - 1) * min(args.max_tokens, 64)
-    rt = GpuRuntime.load(args.model, dtype=args.dtype, device=args.device, max_tokens=args.max_tokens + slack,
-                         max_context=limit)
+    # --max-tokens counts tokens, the cache whole pages a request: every live request (each holds a token at
+    # least; up to 1024 of them) may leave all but one row of its last page empty
+    live = max(1, min(args.max_tokens, 1024))
+    rt = GpuRuntime.load(args.model, dtype=args.dtype, device=args.device,
+                         max_tokens=args.max_tokens + kernels.PAGE * live, max_context=limit, max_sequences=live)
     slots: dict = {}
     for line in stdin:
         line = line.strip()

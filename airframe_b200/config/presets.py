@@ -1,6 +1,6 @@
 """Named configurations for the random-weights mode: the two tiny test
-models and the layer sizes of the released Gemma-2 models, as config.json
-dictionaries.  Nothing here is read by the model code: a configuration always
+models, the layer sizes of the released Gemma-2 models and a small Fiferax, as
+config.json dictionaries.  Nothing here is read by the model code: a configuration always
 reaches it through ``config_from_dict``."""
 from __future__ import annotations
 
@@ -31,6 +31,24 @@ PRESETS = {
                 query_pre_attn_scalar=144, attn_logit_softcapping=50.0, final_logit_softcapping=30.0,
                 max_position_embeddings=8192, torch_dtype="bfloat16"),
 }
+
+
+def _fiferax_small() -> dict:
+    """Fiferax with four layers, one of each kind and a second delta rule (sizes of no released model)."""
+    delta = {"heads": 8, "dim": 64, "rank": 32}
+    par = {"left": {"heads": 8, "kv_heads": 2, "dim": 64, "vdim": 64, "mask": {"size": 256},
+                    "rot": {"base": 10000.0, "dims": 32}, "scale": 0.125}, "left_scale": 1.0,
+           "right": {"heads": 8, "dim": 32, "vdim": 64, "decay": [1.0 - 2.0 ** -(3 + h) for h in range(8)]},
+           "right_scale": 1.0}
+    layers = [{"type": "general_delta", "mixer": delta, "mlp": None},
+              {"type": "parallel", "mixer": par, "mlp": {"kind": "dense", "ff": 1536}},
+              {"type": "general_delta", "mixer": delta, "mlp": None},
+              {"type": "mingru", "mixer": {"width": 768}, "mlp": {"kind": "dense", "ff": 1536}}]
+    return {"architecture": "Fiferax", "vocab": 8192, "width": 512, "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-6}, "layers": layers}
+
+
+PRESETS["fiferax-small"] = _fiferax_small()
 
 
 def preset(name: str) -> dict:

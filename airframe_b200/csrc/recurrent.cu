@@ -451,10 +451,15 @@ static int launch_scan(const AfScanArgs& a, int mode, dim3 grid, int threads, si
 // has fewer, the blocks take fewer columns each.
 static void scan_cut(int mode, int dk, int dv, bool vec, long long units, int want_blocks, int* R, int* P, int* CT,
                      int* CH) {
-  int r = 4;
-  while (r < 32 && (dk + r - 1) / r > 8) r *= 2;            // up to eight lanes a column while a lane holds up to 32
-  int p = 1;
-  while (p * r < dk && p < 32) p *= 2;
+  // A token costs a lane a chain of instructions as long as its share of the key channels: while the whole
+  // step has no more threads than two blocks an SM hold (a prompt or two: all blocks run at once), a column gets up to sixteen lanes;
+  // with more work than that, eight lanes at most (fewer shuffles and less staging a state element).
+  int r = 4, p = 1;
+  for (;; r *= 2) {
+    p = 1;
+    while (p * r < dk && p < 32) p *= 2;
+    if (r == 32 || (p * r >= dk && (p <= 8 || (p <= 16 && units * dv * p <= (long long)want_blocks * 256)))) break;
+  }
   int ct = 128 / p;                                          // 128 threads a block
   while (ct > 4 && ct / 2 >= dv && (ct / 2) * p >= 32) ct /= 2;   // (no wider than the state's columns need; whole warps)
   while (ct > 4 && (ct / 2) * p >= 64 && units * ((dv + ct - 1) / ct) < want_blocks) ct /= 2;

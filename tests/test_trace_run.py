@@ -96,9 +96,9 @@ def test_replay_whole_tail_and_batches(name, dtype, tmp_path):
 
 def test_replay_refuses_more_tokens_than_it_was_sized_for(tmp_path):
     folder = make_folder(CONFIGS["B"], seed=1, root=tmp_path / "model")
-    steps = [{"step": 0, "entries": [{"id": "a", "tokens": list(range(65)), "want": []},
-                                     {"id": "b", "tokens": [1], "want": []}], "end": []}]
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": [5], "want": []}, {"id": "b", "tokens": [1], "want": []},
+                                     {"id": "c", "tokens": [2], "want": []}], "end": []}]
     proc = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype",
-                           "float32", "--out", str(tmp_path / "o"), "--max-tokens", "128"],
+                           "float32", "--out", str(tmp_path / "o"), "--max-tokens", "2"],
                           input=json.dumps(steps[0]) + "\n", capture_output=True, text=True, timeout=900)
     assert proc.returncode != 0 and "CacheFull" in proc.stderr
