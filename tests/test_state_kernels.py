@@ -69,7 +69,7 @@ def test_delta_rule_scan(heads, dk, dv):
     state[0].zero_()
     got = []
     at = 0
-    for n in (20, 16, 1):
+    for n in (19, 13, 2, 1, 2):
         rows = [t[at:at + n].contiguous() for t in dev]
         pad = [torch.cat([t, torch.ones(1, t.shape[1], device=DEV)]) for t in rows]
         o = torch.full((n + 1, heads * dv), 7.0, device=DEV)

@@ -55,7 +55,19 @@ FX_C = {
     ],
 }
 
-CONFIGS = {"A": FX_A, "B": FX_B, "C": FX_C}
+# nothing divides by four: a width of 50, key sizes of 10 and 6 (scalar fetches in every kernel, plain products
+# in bfloat16 too), no rotation at all in one attention and a window of one token (a token sees itself alone)
+FX_D = {
+    "architecture": "Fiferax", "vocab": 97, "width": 50, "embedding": {"scale": 2.0}, "norm": {"eps": 1e-4},
+    "layers": [
+        _layer("parallel", _parallel(3, 1, 10, 1, 0, 10.0, 0.5, 0.5, 1, 6, 10, [0.9], 2.0)),
+        _layer("general_delta", {"heads": 3, "dim": 10, "rank": 2}, ff=36),
+        _layer("mingru", {"width": 30}),
+        _layer("parallel", _parallel(2, 2, 14, 33, 6, 77.0, 0.3, 1.0, 2, 10, 6, [0.7, 1.0], 1.0), ff=22),
+    ],
+}
+
+CONFIGS = {"A": FX_A, "B": FX_B, "C": FX_C, "D": FX_D}
 
 
 def make_folder(cfg_dict, seed=0, store_dtype="bfloat16", root=None, edit=None):
