@@ -103,12 +103,25 @@ struct AfScanArgs {
   int silu;
 };
 
+// Floats of padding behind a lane's run of R staged key channels: the 16-byte reads of a quarter warp (eight
+// lanes, a run apart) then fall into different banks.  Runs of four floats lie side by side as they are.
+#define AF_SCAN_PAD(R) ((R) == 4 ? 0 : 4)
 #define AF_SCAN_PREFETCH 24    // values a thread holds in registers for the chunk after the current one
 #define AF_SCAN_VEC_ITEMS 2    // the same in 16-byte pieces, per vector, where the sizes allow whole pieces
 
+// Sum over the P lanes that share a column (P a power of two up to 32; the lanes of a group are neighbours).
+__device__ __forceinline__ float lanes_sum(float v, int P) {
+  if (P > 1) v += __shfl_xor_sync(0xffffffffu, v, 1);
+  if (P > 2) v += __shfl_xor_sync(0xffffffffu, v, 2);
+  if (P > 4) v += __shfl_xor_sync(0xffffffffu, v, 4);
+  if (P > 8) v += __shfl_xor_sync(0xffffffffu, v, 8);
+  if (P > 16) v += __shfl_xor_sync(0xffffffffu, v, 16);
+  return v;
+}
+
 // One block per (column tile, head, sequence); thread = (column, lane of the column).  The block walks
 // the sequence's tokens in chunks: while it scans a chunk out of shared memory, the next chunk's vectors
-// are on their way into registers.  Key channel c lives at (c / R) (R + 4) + c % R of a staged vector (four
+// are on their way into registers.  Key channel c lives at (c / R) (R + pad) + c % R of a staged vector (four
 // floats of padding per lane's run keep the 16-byte reads of a quarter warp in different banks).
 template <int R, int MODE, bool VEC>
 __global__ void __launch_bounds__(256)
@@ -117,7 +130,7 @@ state_scan_kernel(AfScanArgs a) {
   extern __shared__ __align__(16) float smem[];
   const int P = a.lanes, CT = a.cols, CH = a.chunk, dk = a.dk, dv = a.dv;
   const int NV = MODE == AF_SCAN_DELTA ? 5 : 2;             // staged key-sized vectors: r, k (, w, u, au)
-  const int dkp = P * (R + 4);
+  const int dkp = P * (R + AF_SCAN_PAD(R));
   const int tok_floats = NV * dkp + CT;                     // a token's staged floats: the vectors, then its v tile
   const int buf_floats = CH * tok_floats;
   const int tid = threadIdx.x, nthr = blockDim.x;
@@ -182,7 +195,7 @@ state_scan_kernel(AfScanArgs a) {
       const int tt = idx / dkq, c = (idx - tt * dkq) * 4;
       ftt[e] = idx < CH * dkq ? tt : CH;                     // (CH: never among a chunk's tokens)
       fgo[e] = h * dk + c;
-      fso[e] = tt * tok_floats + (c / R) * (R + 4) + c % R;
+      fso[e] = tt * tok_floats + (c / R) * (R + AF_SCAN_PAD(R)) + c % R;
     }
 #pragma unroll
     for (int e = 0; e < FV; ++e) {
@@ -254,7 +267,7 @@ state_scan_kernel(AfScanArgs a) {
           bool act = a.silu != 0;
           if (x < NV * dk) {
             const int vec = x / dk, c = x - vec * dk;
-            at = vec * dkp + (c / R) * (R + 4) + c % R;
+            at = vec * dkp + (c / R) * (R + AF_SCAN_PAD(R)) + c % R;
             act = act && vec < 2;
           } else {
             at = NV * dkp + x - NV * dk;
@@ -279,7 +292,7 @@ state_scan_kernel(AfScanArgs a) {
     if (n1 > 0) fetch(t1, n1);                               // under the scan of this chunk
 #pragma unroll 2
     for (int tt = 0; tt < n; ++tt) {
-      const float* tk = buf + tt * tok_floats + part * (R + 4);
+      const float* tk = buf + tt * tok_floats + part * (R + AF_SCAN_PAD(R));
       const float vj = buf[tt * tok_floats + NV * dkp + col];
       float rv[R], kv[R];
 #pragma unroll
@@ -301,8 +314,7 @@ state_scan_kernel(AfScanArgs a) {
           d0 += uv[i] * S[i];
           d1 += uv[i + 1] * S[i + 1];
         }
-        float dot = d0 + d1;
-        for (int o = 1; o < P; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        const float dot = lanes_sum(d0 + d1, P);
 #pragma unroll
         for (int i = 0; i < R; ++i) S[i] = wv[i] * S[i] - av[i] * dot + kv[i] * vj;
       } else {
@@ -315,8 +327,7 @@ state_scan_kernel(AfScanArgs a) {
         o0 += rv[i] * S[i];
         o1 += rv[i + 1] * S[i + 1];
       }
-      float o = o0 + o1;
-      for (int s = 1; s < P; s <<= 1) o += __shfl_xor_sync(0xffffffffu, o, s);
+      const float o = lanes_sum(o0 + o1, P);
       if (part == 0 && col_on) a.out[(size_t)(t0 + tt) * a.out_ts + h * dv + j] = o;
     }
     t0 = t1;
@@ -394,8 +405,7 @@ state_step_kernel(AfScanArgs a, int vec) {
     float d0 = 0.f, d1 = 0.f;
 #pragma unroll
     for (int i = 0; i < R; i += 2) d0 += uv[i] * S[i], d1 += uv[i + 1] * S[i + 1];
-    float dot = d0 + d1;
-    for (int o = 1; o < P; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    const float dot = lanes_sum(d0 + d1, P);
 #pragma unroll
     for (int i = 0; i < R; ++i) S[i] = wv[i] * S[i] - av[i] * dot + kv[i] * vj;
   } else {
@@ -405,8 +415,7 @@ state_step_kernel(AfScanArgs a, int vec) {
   float o0 = 0.f, o1 = 0.f;
 #pragma unroll
   for (int i = 0; i < R; i += 2) o0 += rv[i] * S[i], o1 += rv[i + 1] * S[i + 1];
-  float o = o0 + o1;
-  for (int sft = 1; sft < P; sft <<= 1) o += __shfl_xor_sync(0xffffffffu, o, sft);
+  const float o = lanes_sum(o0 + o1, P);
   if (part == 0 && col_on) a.out[t * a.out_ts + h * dv + j] = o;
   if (!col_on) return;
   if (vec) {
@@ -464,7 +473,7 @@ static void scan_cut(int mode, int dk, int dv, bool vec, long long units, int wa
   while (ct > 4 && ct / 2 >= dv && (ct / 2) * p >= 32) ct /= 2;   // (no wider than the state's columns need; whole warps)
   while (ct > 4 && (ct / 2) * p >= 64 && units * ((dv + ct - 1) / ct) < want_blocks) ct /= 2;
   const int nv = mode == AF_SCAN_DELTA ? 5 : 2;
-  const int tok_vals = nv * dk + ct, tok_floats = nv * p * (r + 4) + ct;
+  const int tok_vals = nv * dk + ct, tok_floats = nv * p * (r + AF_SCAN_PAD(r)) + ct;
   const int threads = ct * p;
   int ch = 16;
   while (ch > 1 && 2 * ch * tok_floats * 4 > 96 * 1024) ch /= 2;
@@ -517,7 +526,7 @@ AF_EXPORT int af_state_scan(int mode, const float* r, long long r_ts, const floa
       default: return launch_step<32>(a, mode, vec ? 1 : 0, grid, CT * P, stream);
     }
   }
-  const size_t smem = (size_t)2 * CH * (nv * P * (R + 4) + CT) * sizeof(float);
+  const size_t smem = (size_t)2 * CH * (nv * P * (R + AF_SCAN_PAD(R)) + CT) * sizeof(float);
   const dim3 grid((dv + CT - 1) / CT, heads, n_seqs);
   const int threads = CT * P;
   if (vec) {
