@@ -81,6 +81,9 @@ AF_EXPORT int af_delta_prep(float* out, const float* proj, long long ld, int off
 // ---------------------------------------------------------------- the scan over a matrix state
 
 enum AfScanMode { AF_SCAN_DECAY = 0, AF_SCAN_DELTA = 1 };
+// (inside the library: the decay recurrence whose r, k and v pass through SiLU as they are read; a kernel of
+// its own, so that the others carry no exponentials)
+#define AF_SCAN_DECAY_SILU 2
 
 // The vectors of a token and head that the scan reads (float rows; `*_ts` is the distance between
 // tokens in elements; head h's piece starts h * dk (h * dv for v) behind the pointer):
@@ -127,6 +130,7 @@ template <int R, int MODE, bool VEC>
 __global__ void __launch_bounds__(256)
 state_scan_kernel(AfScanArgs a) {
   pdl_launch_dependents();
+  constexpr bool SILU = MODE == AF_SCAN_DECAY_SILU;
   extern __shared__ __align__(16) float smem[];
   const int P = a.lanes, CT = a.cols, CH = a.chunk, dk = a.dk, dv = a.dv;
   const int NV = MODE == AF_SCAN_DELTA ? 5 : 2;             // staged key-sized vectors: r, k (, w, u, au)
@@ -163,7 +167,7 @@ state_scan_kernel(AfScanArgs a) {
 #pragma unroll
     for (int i = 0; i < R; ++i) S[i] = (col_on && part * R + i < dk) ? st[i] : 0.f;
   }
-  const float dec = MODE == AF_SCAN_DECAY ? a.decay[h] : 0.f;
+  const float dec = MODE != AF_SCAN_DELTA ? a.decay[h] : 0.f;
   auto keep_state = [&]() {
     if (!col_on) return;
     if (vec) {
@@ -253,10 +257,10 @@ state_scan_kernel(AfScanArgs a) {
 #pragma unroll
         for (int e = 0; e < FE; ++e)
           if (ftt[e] < n)
-            *reinterpret_cast<float4*>(buf + fso[e] + v * dkp) = (a.silu && v < 2) ? act4(pq[v][e]) : pq[v][e];
+            *reinterpret_cast<float4*>(buf + fso[e] + v * dkp) = (SILU && v < 2) ? act4(pq[v][e]) : pq[v][e];
 #pragma unroll
       for (int e = 0; e < FV; ++e)
-        if (vtt[e] < n) *reinterpret_cast<float4*>(buf + vso[e]) = a.silu ? act4(pvq[e]) : pvq[e];
+        if (vtt[e] < n) *reinterpret_cast<float4*>(buf + vso[e]) = SILU ? act4(pvq[e]) : pvq[e];
     } else {
 #pragma unroll
       for (int e = 0; e < AF_SCAN_PREFETCH; ++e) {
@@ -264,7 +268,7 @@ state_scan_kernel(AfScanArgs a) {
         if (idx < n * tok_vals) {
           const int tt = idx / tok_vals, x = idx - tt * tok_vals;
           int at;
-          bool act = a.silu != 0;
+          bool act = SILU;
           if (x < NV * dk) {
             const int vec = x / dk, c = x - vec * dk;
             at = vec * dkp + (c / R) * (R + AF_SCAN_PAD(R)) + c % R;
@@ -344,6 +348,7 @@ template <int R, int MODE>
 __global__ void __launch_bounds__(128)
 state_step_kernel(AfScanArgs a, int vec) {
   pdl_launch_dependents();
+  constexpr bool SILU = MODE == AF_SCAN_DECAY_SILU;
   const int P = a.lanes, CT = a.cols, dk = a.dk, dv = a.dv;
   const int tid = threadIdx.x;
   const int part = tid % P, col = tid / P;
@@ -372,7 +377,7 @@ state_step_kernel(AfScanArgs a, int vec) {
 #pragma unroll
     for (int i = 0; i < R; ++i) S[i] = (col_on && c0 + i < dk) ? st[i] : 0.f;
   }
-  const float dec = MODE == AF_SCAN_DECAY ? a.decay[h] : 0.f;
+  const float dec = MODE != AF_SCAN_DELTA ? a.decay[h] : 0.f;
   pdl_wait();
   auto piece = [&](const float* p, float* dst, bool act) {
     p += h * dk + c0;
@@ -393,10 +398,10 @@ state_step_kernel(AfScanArgs a, int vec) {
     }
   };
   float rv[R], kv[R];
-  piece(a.r + t * a.r_ts, rv, a.silu != 0);
-  piece(a.k + t * a.k_ts, kv, a.silu != 0);
+  piece(a.r + t * a.r_ts, rv, SILU);
+  piece(a.k + t * a.k_ts, kv, SILU);
   float vj = col_on ? a.v[t * a.v_ts + h * dv + j] : 0.f;
-  if (a.silu) vj = vj / (1.f + expf(-vj));
+  if (SILU) vj = vj / (1.f + expf(-vj));
   if (MODE == AF_SCAN_DELTA) {
     float wv[R], uv[R], av[R];
     piece(a.w + t * a.w_ts, wv, false);
@@ -432,25 +437,29 @@ state_step_kernel(AfScanArgs a, int vec) {
 template <int R>
 static int launch_step(const AfScanArgs& a, int mode, int vec, dim3 grid, int threads, cudaStream_t stream) {
   if (mode == AF_SCAN_DELTA) af_launch(state_step_kernel<R, AF_SCAN_DELTA>, grid, dim3(threads), 0, stream, a, vec);
+  else if (a.silu) af_launch(state_step_kernel<R, AF_SCAN_DECAY_SILU>, grid, dim3(threads), 0, stream, a, vec);
   else af_launch(state_step_kernel<R, AF_SCAN_DECAY>, grid, dim3(threads), 0, stream, a, vec);
   AF_CHECK_LAUNCH("af_state_scan");
 }
 
 template <int R, bool VEC>
 static int launch_scan(const AfScanArgs& a, int mode, dim3 grid, int threads, size_t smem, cudaStream_t stream) {
-  static bool raised[2][AF_MAX_DEVICES];
+  static bool raised[3][AF_MAX_DEVICES];
   auto k0 = state_scan_kernel<R, AF_SCAN_DECAY, VEC>;
   auto k1 = state_scan_kernel<R, AF_SCAN_DELTA, VEC>;
+  auto k2 = state_scan_kernel<R, AF_SCAN_DECAY_SILU, VEC>;
+  const int which = mode == AF_SCAN_DELTA ? 1 : (a.silu ? 2 : 0);
   if (smem > 48 * 1024) {
     const int dev = af_current_device();
     if (dev < 0) return -1;
-    if (af_first_on_device(raised[mode], dev)) {
-      cudaError_t e = cudaFuncSetAttribute(mode == AF_SCAN_DELTA ? k1 : k0, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (af_first_on_device(raised[which], dev)) {
+      cudaError_t e = cudaFuncSetAttribute(which == 1 ? k1 : which == 2 ? k2 : k0, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            96 * 1024);
       if (e != cudaSuccess) return af_fail((int)e, "af_state_scan: %s", cudaGetErrorString(e));
     }
   }
-  if (mode == AF_SCAN_DELTA) af_launch(k1, grid, dim3(threads), smem, stream, a);
+  if (which == 1) af_launch(k1, grid, dim3(threads), smem, stream, a);
+  else if (which == 2) af_launch(k2, grid, dim3(threads), smem, stream, a);
   else af_launch(k0, grid, dim3(threads), smem, stream, a);
   AF_CHECK_LAUNCH("af_state_scan");
 }
@@ -492,6 +501,7 @@ AF_EXPORT int af_state_scan(int mode, const float* r, long long r_ts, const floa
                             int dk, int dv, int silu, cudaStream_t stream) {
   if (n_seqs == 0) return 0;
   AF_REQUIRE(mode == AF_SCAN_DECAY || mode == AF_SCAN_DELTA, "af_state_scan: mode %d", mode);
+  AF_REQUIRE(!(mode == AF_SCAN_DELTA && silu), "af_state_scan: the delta rule takes its vectors as they are");
   AF_REQUIRE(n_seqs > 0 && heads > 0 && dk > 0 && dv > 0 && dk <= 1024, "af_state_scan: bad sizes (key size up to 1024)");
   AF_REQUIRE(n_seqs < 65536 && heads < 65536, "af_state_scan: too many sequences or heads for one grid");
   AfScanArgs a;
