@@ -345,7 +345,7 @@ state_scan_kernel(AfScanArgs a) {
 // sequence) as above, but nothing is staged: the token's vectors go from memory to the lanes' registers, the
 // state's tile is read, updated and written back.  `vec`: whole 16-byte pieces.
 template <int R, int MODE>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 state_step_kernel(AfScanArgs a, int vec) {
   pdl_launch_dependents();
   constexpr bool SILU = MODE == AF_SCAN_DECAY_SILU;
@@ -465,8 +465,7 @@ static int launch_scan(const AfScanArgs& a, int mode, dim3 grid, int threads, si
 }
 
 // The cut of a scan: R key channels a lane, P lanes a column, CT columns a block, CH tokens a chunk.
-// `vec`: the vectors are fetched in 16-byte pieces.  `want_blocks`: blocks that fill the device; while the grid
-// has fewer, the blocks take fewer columns each.
+// `vec`: the vectors are fetched in 16-byte pieces.  `want_blocks`: the device's SMs (what "a small step" is measured by).
 static void scan_cut(int mode, int dk, int dv, bool vec, long long units, int want_blocks, int* R, int* P, int* CT,
                      int* CH) {
   // A token costs a lane a chain of instructions as long as its share of the key channels: while the whole
@@ -478,9 +477,10 @@ static void scan_cut(int mode, int dk, int dv, bool vec, long long units, int wa
     while (p * r < dk && p < 32) p *= 2;
     if (r == 32 || (p * r >= dk && (p <= 8 || (p <= 16 && units * dv * p <= (long long)want_blocks * 256)))) break;
   }
-  int ct = 128 / p;                                          // 128 threads a block
+  // 256 threads a block (512 measured the same or slower): every block of a head stages the head's vectors for itself, so wide tiles of columns
+  // (few blocks a head, many warps a block) cost less than narrow ones, also where that leaves SMs without a block
+  int ct = 256 / p;
   while (ct > 4 && ct / 2 >= dv && (ct / 2) * p >= 32) ct /= 2;   // (no wider than the state's columns need; whole warps)
-  while (ct > 4 && (ct / 2) * p >= 64 && units * ((dv + ct - 1) / ct) < want_blocks) ct /= 2;
   const int nv = mode == AF_SCAN_DELTA ? 5 : 2;
   const int tok_vals = nv * dk + ct, tok_floats = nv * p * (r + AF_SCAN_PAD(r)) + ct;
   const int threads = ct * p;
