@@ -3,7 +3,7 @@ layer by layer in config.json (``layers[i].type``):
 
 ``general_delta``  the generalized delta rule over a matrix state per head;
 ``parallel``       windowed softmax attention (query/key norm, rotary on part of a
-                   head, values that are the keys as projected) beside linear attention
+                   head, values taken from the raw key projection) beside linear attention
                    with a decay per head, summed with a scale each;
 ``mingru``         a gated recurrence over a vector state.
 
@@ -61,7 +61,7 @@ class FiferaxConfig(ModelConfig):
             if heads % groups:
                 raise ConfigError(f"{where}.left: {heads} heads are not a multiple of {groups} kv_heads")
             if left.integer("vdim", dim, minimum=1) != dim:
-                raise ConfigError(f"{where}.left: the values are the keys as projected, so vdim must equal dim {dim}")
+                raise ConfigError(f"{where}.left: the values come from the key projection, so vdim must equal dim {dim}")
             left.number("scale")
             KeyReader(left.data.get("mask"), where + ".left.mask").integer("size", minimum=1)
             rot = KeyReader(left.data.get("rot"), where + ".left.rot")

@@ -456,7 +456,7 @@ AF_EXPORT int af_attn_decode_plain(void* out, int out_stride, const void* q, int
 // ---------------------------------------------------------------- norm + rope + cache write from a projection
 
 // Queries and keys that are normalised per head before they are rotated, and values that may be the
-// keys as projected.  The projection row of a token is float [q heads | k heads (| v heads)]; a warp per
+// raw key projection.  The projection row of a token is float [q heads | k heads (| v heads)]; a warp per
 // (token, q or k head):
 //   n = x * rsqrt(mean(x^2) + eps) * weight   (weight of head_dim values shared by the heads; none: n = x)
 //   the first rot_dim elements of n rotated by position * frequency (32-bit), the rest kept

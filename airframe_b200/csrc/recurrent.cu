@@ -88,7 +88,7 @@ enum AfScanMode { AF_SCAN_DECAY = 0, AF_SCAN_DELTA = 1 };
 // The vectors of a token and head that the scan reads (float rows; `*_ts` is the distance between
 // tokens in elements; head h's piece starts h * dk (h * dv for v) behind the pointer):
 //   DECAY:  S <- decay[h] S + k v^T                          o = S^T q     (q = `r`)
-//   DELTA:  S <- diag(w) S - au (u^T S) + k v^T              o = S^T r     (both terms read the old S)
+//   DELTA:  S <- diag(w) S - au (u^T S) + k v^T              o = S^T r     (decay and removal act on the S before the token)
 // With `silu` the r, k and v values go through x / (1 + exp(-x)) as they are read.
 struct AfScanArgs {
   const float *r, *k, *v, *w, *u, *au;
@@ -558,7 +558,7 @@ AF_EXPORT int af_state_scan(int mode, const float* r, long long r_ts, const floa
 // ---------------------------------------------------------------- the output of a state mixer
 
 // y[t][i] = o[t][i] * rsqrt(mean over i's group of o^2 + eps) * w[i] * sigmoid(gate[t][i]): a norm over groups
-// of `group` values (a head, or the whole row) with a plain weight, times a gate.  One block per token.
+// of `group` values (a head, or the whole row) with a weight vector (no offset), times a gate.  One block per token.
 template <typename TY>
 __global__ void __launch_bounds__(256)
 gated_group_norm_kernel(TY* __restrict__ y, const float* __restrict__ o, const float* __restrict__ w,

@@ -730,7 +730,7 @@ def state_scan(mode: str, out, r, k, v, state, batch, heads: int, dk: int, dv: i
     the state that earlier steps left in ``state`` (float32 [slots, heads, dv, dk]; left updated):
 
     ``decay``: S <- decay[h] S + k v^T, o = S^T r;
-    ``delta``: S <- diag(w) S - au (u^T S) + k v^T, o = S^T r (both terms read the old S).
+    ``delta``: S <- diag(w) S - au (u^T S) + k v^T, o = S^T r (the decay and the removal act on the state before the token).
 
     r, k, w, u, au: float32 rows [T, heads * dk] (column sections allowed), v [T, heads * dv], out float32
     [T, heads * dv].  ``silu``: r, k and v pass through x * sigmoid(x) as they are read.  A step in which
@@ -798,7 +798,7 @@ def qk_norm_rope_store(qkv, proj, batch, nq: int, nkv: int, hd: int, inv_freq, r
     """From float32 projection rows [q heads | k heads (| v heads)]: q and k heads normalised per head
     (x * rsqrt(mean x^2 + eps) * weight, the weight of ``hd`` values shared by the heads; no weights: as
     they are), their first ``rot_dim`` elements rotated, into the packed rows ``qkv`` [q | k | v] of the
-    compute dtype; the value heads are the k heads as projected (``v_from_k``) or the projection's own.
+    compute dtype; the value heads are the raw k heads of the projection (``v_from_k``) or the projection's own.
     With ``kv`` (the layer's view of its cache pages) k and v also go to each token's row of its page."""
     T = proj.shape[0]
     width_in = (nq + nkv) * hd if v_from_k else (nq + 2 * nkv) * hd

@@ -10,7 +10,7 @@ head_dim^-0.5 and has no window; both are parameters here.
 
 Two more options, for designs that have them: ``qk_norm`` (q and k heads are
 RMS-normed per head with a weight of head_dim values that all heads share,
-before any rotation) and values that are the keys as projected (no
+before any rotation) and values taken from the raw key projection (no
 ``v_weight``: v = W_k h, before norm and rotation).  With either, the
 projection goes into 32-bit rows and one kernel norms, rotates, packs
 [q | k | v] and writes the cache.
@@ -162,7 +162,7 @@ class Attention(Mixer):
 
     def _project_norm_pack(self, x, batch, view):
         """The projection in 32-bit rows; q and k heads normed and rotated, the values taken
-        (from the keys as projected, or their own heads), all packed and the cache written: one kernel."""
+        (from the raw key projection, or their own heads), all packed and the cache written: one kernel."""
         nq, nkv, hd = self.nq, self.nkv, self.hd
         proj = linear(x, self.w_qkv, out_dtype=torch.float32)
         qkv = torch.empty(x.shape[0], (nq + 2 * nkv) * hd, dtype=x.dtype, device=x.device)

@@ -9,13 +9,13 @@ key u = k / sqrt(|k|^2 + key_eps):
 
     S <- diag(w) S - (a * u)(u^T S) + k v^T        o = S^T r
 
-(both terms read the old S).  w = exp(-decay_scale * sigmoid(W2 tanh(W1 h) + w0)),
+(the decay and the removal act on the state before the token).  w = exp(-decay_scale * sigmoid(W2 tanh(W1 h) + w0)),
 a = sigmoid(Wa h + ba).  Each head's o is divided by its root mean square, times a
-plain weight, times sigmoid(Wg h), then the output projection.
+weight vector (no offset), times sigmoid(Wg h), then the output projection.
 
 ``lightning_attention``: linear attention with a fixed decay per head:
 q, k, v = silu of their projections, S <- decay_h S + k v^T, o = S^T q; the heads
-together are RMS-normed with a plain weight, times sigmoid(Wg h), then projected.
+together are RMS-normed with a weight vector (no offset), times sigmoid(Wg h), then projected.
 
 ``mingru``: a gated recurrence over a vector: z = sigmoid(Wz h + bz),
 c = Wx h + bx, candidate = c + 1/2 where c >= 0 and sigmoid(c) below,

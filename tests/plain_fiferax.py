@@ -109,7 +109,7 @@ def norm_rope_attention(h, W, p, m, eps):
     H, G, d = m["heads"], m["kv_heads"], m["dim"]
     q = (h @ W[p + "q"].T).view(T, H, d)
     k = (h @ W[p + "k"].T).view(T, G, d)
-    v = k.clone()                                   # the values are the keys as projected
+    v = k.clone()                                   # values: the raw key projection
     pos = torch.arange(T)
     q = rotate_half(rms(q, eps, W[p + "q.norm"]), pos, m["rot"]["base"], m["rot"]["dims"])
     k = rotate_half(rms(k, eps, W[p + "k.norm"]), pos, m["rot"]["base"], m["rot"]["dims"])

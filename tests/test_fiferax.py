@@ -316,3 +316,34 @@ def test_trace_replay_of_a_fiferax_folder(tmp_path, tmp_path_factory):
     assert rel_err(s0, ra[[0, 17]]) < VS_PLAIN["float32"]
     assert rel_err(s1, torch.stack([ra[18], rb[6]])) < VS_PLAIN["float32"]
     assert not (tmp_path / "2.f32").exists()
+
+
+@gpu
+def test_long_prompt_at_layer_sizes_beyond_the_plain_implementation(tmp_path_factory):
+    """The named small configuration (width 512, head size 64, a window of 256) on a prompt of 2,500 tokens
+    that laps the window's ring ten times, then 70 single tokens: too long for the plain implementation, so
+    the engine is held against itself: the 32-bit logits must not depend on where the prompt ends and the
+    single tokens begin, and bfloat16 must agree with 32-bit within its rounding."""
+    from airframe_b200.config.presets import preset
+    from tiny_fiferax import make_folder as make
+    folder = make(preset("fiferax-small"), seed=4, root=tmp_path_factory.mktemp("fxsmall"))
+    from airframe_b200.engine import GpuRuntime, StepEntry
+    ids = replay.random_ids(8192, 2570, 17)
+    want = [0, 1, 255, 256, 257, 1023, 2047, 2499]
+
+    def run(dtype, cut):
+        rt = GpuRuntime.load(folder, dtype=dtype, max_tokens=64 * 48, max_context=4096)
+        s = rt.engine.take_slot()
+        out = [rt.step([StepEntry(s, ids[:cut], [w for w in want if w < cut])]).cpu()]
+        for t in ids[cut:]:
+            out.append(rt.step([StepEntry(s, [t], [0])]).cpu())
+        rt.engine.free_slot(s)
+        return torch.cat(out)
+
+    a = run("float32", 2500)
+    assert torch.isfinite(a).all()
+    b = run("float32", 2540)
+    # the last 30 tokens were single tokens in both runs; tokens 2500..2539 single in one, of the prompt in the other
+    assert rel_err(b[-30:], a[-30:]) < 1e-4
+    c = run("bfloat16", 2500)
+    assert rms_rel(c, a) < 3e-2
