@@ -26,6 +26,10 @@ prompts of 1,024-8,192 tokens and 128 decode steps (a prompt is at most as long 
 leaves room for the decoded tokens in the context of 8192).  Their prefill figure is
 the whole unequal batch in one step.  Bytes and flops of the rooflines are asked of
 the model's parts (``Model.decode_bytes``, ``Model.prefill_flops``).
+
+``--fiferax all|w1024|w2304|w4096`` (not the default run) prints, for layer sizes like a real model's, one line
+for Fiferax and one for Gemma-2 of equal width, depth, feed-forward and vocabulary: prefill of one prompt of
+2,048 tokens, decode at batch 8 after such prompts, and the device time of every kernel of both.
 """
 from __future__ import annotations
 

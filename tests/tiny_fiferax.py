@@ -50,7 +50,7 @@ FX_C = {
     "architecture": "Fiferax", "vocab": 500, "width": 256, "embedding": {"scale": 0.5}, "norm": {"eps": 1e-6},
     "layers": [
         _layer("general_delta", {"heads": 2, "dim": 128, "rank": 24}, ff=320),
-        _layer("parallel", _parallel(4, 1, 128, 100, 64, 20000.0, 0.09, 0.8, 2, 128, 128, [0.98, 0.9995], 0.9)),
+        _layer("parallel", _parallel(4, 1, 128, 100, 64, 30000.0, 0.09, 0.75, 2, 128, 128, [0.98, 0.9995], 0.85)),
         _layer("mingru", {"width": 512}, ff=256),
     ],
 }
