@@ -153,7 +153,7 @@ def load(c, dtype, max_tokens=64 * 24, **kw):
 
 
 @gpu
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_whole_prompt_and_token_by_token(name, dtype, tmp_path_factory):
     """A prompt in one step; the same tokens with the last 40 one by one (the captured decode step);
     and a prompt of one token followed by single tokens only."""

@@ -67,7 +67,17 @@ FX_D = {
     ],
 }
 
-CONFIGS = {"A": FX_A, "B": FX_B, "C": FX_C, "D": FX_D}
+# odd everywhere: a width of 51, head sizes of 9, 7, 5 and 3, a feed-forward of 17, 31 tokens
+FX_E = {
+    "architecture": "Fiferax", "vocab": 31, "width": 51, "embedding": {"scale": 1.5}, "norm": {"eps": 1e-5},
+    "layers": [
+        _layer("general_delta", {"heads": 1, "dim": 7, "rank": 1}),
+        _layer("parallel", _parallel(3, 3, 9, 4, 4, 50.0, 0.6, 0.9, 3, 5, 3, [0.5, 0.9, 0.99], 1.1), ff=17),
+        _layer("mingru", {"width": 13}, ff=9),
+    ],
+}
+
+CONFIGS = {"A": FX_A, "B": FX_B, "C": FX_C, "D": FX_D, "E": FX_E}
 
 
 def make_folder(cfg_dict, seed=0, store_dtype="bfloat16", root=None, edit=None):
