@@ -53,8 +53,9 @@ def main(argv=None, stdin=None, stdout=None) -> int:
     out_dir.mkdir(parents=True, exist_ok=True)
     limit = config_from_folder(args.model).model_spec().max_positions
     # --max-tokens counts tokens, the cache whole pages a request: every live request (each holds a token at
-    # least; up to 1024 of them) may leave all but one row of its last page empty
-    live = max(1, min(args.max_tokens, 1024))
+    # least; up to 256 of them, each with a state of its own in every layer that keeps one) may leave all but one row
+    # of its last page empty
+    live = max(1, min(args.max_tokens, 256))
     rt = GpuRuntime.load(args.model, dtype=args.dtype, device=args.device,
                          max_tokens=args.max_tokens + kernels.PAGE * live, max_context=limit, max_sequences=live)
     slots: dict = {}
