@@ -3,7 +3,8 @@ run of a layer, each sequence with its own length.
 
 Storage is paged.  A *group* holds the runs of layers with the same need
 (number of kv heads, head size, all keys or a window of them).  Each group
-owns K and V pages ``[runs, pages, kv_heads, PAGE, head_dim]`` and a page
+owns K and V pages ``[runs, pages, kv_heads, PAGE, head_dim]`` (value rows may
+have a size of their own, or be left out when a mixer keeps them inside its key rows) and a page
 table ``[slots, pages per sequence]``.  A group with a window keeps rows
 modulo ``ring_rows`` (the window rounded up to whole pages), so a sequence
 never holds more than ``ring_rows`` rows there.  Pages are taken as a
@@ -58,9 +59,10 @@ class KVGroup:
         self.dirty = set()
         self.k = self.v = self.table = None
         if device is not None:
-            shape = (len(self.run_ids), n_pages, need.num_kv_heads, PAGE, need.head_dim)
-            self.k = torch.zeros(shape, dtype=dtype, device=device)
-            self.v = torch.zeros(shape, dtype=dtype, device=device)
+            shape = (len(self.run_ids), n_pages, need.num_kv_heads, PAGE)
+            self.k = torch.zeros((*shape, need.head_dim), dtype=dtype, device=device)
+            if need.value_size:        # (0: the values lie inside the key rows)
+                self.v = torch.zeros((*shape, need.value_size), dtype=dtype, device=device)
             self.table = torch.full((n_slots, self.pages_per_seq), -1, dtype=torch.int32, device=device)
 
     def rows_held(self, length: int) -> int:
@@ -111,7 +113,7 @@ class KVGroup:
 
     def bytes_per_token(self) -> int:
         el = 2 if self.k is None else self.k.element_size()
-        return 2 * len(self.run_ids) * self.need.num_kv_heads * self.need.head_dim * el
+        return len(self.run_ids) * self.need.num_kv_heads * (self.need.head_dim + self.need.value_size) * el
 
 
 @dataclass
@@ -182,7 +184,8 @@ class SequenceCache:
             if kv_need is not None:
                 if src_need is None:
                     raise ValueError(f"run {run} reads keys and values of run {src}, which keeps none")
-                if (src_need.num_kv_heads, src_need.head_dim) != (kv_need.num_kv_heads, kv_need.head_dim):
+                if (src_need.num_kv_heads, src_need.head_dim, src_need.value_size) != \
+                        (kv_need.num_kv_heads, kv_need.head_dim, kv_need.value_size):
                     raise ValueError(f"run {run} reads the cache of run {src} with other head sizes")
                 g = self.groups[src_need]
                 i = g.index_of[src]
@@ -272,6 +275,7 @@ class SequenceCache:
     def bytes_allocated(self) -> int:
         n = 0
         for g in self.groups.values():
-            if g.k is not None:
-                n += g.k.numel() * g.k.element_size() * 2
+            for t in (g.k, g.v):
+                if t is not None:
+                    n += t.numel() * t.element_size()
         return n

@@ -1,6 +1,7 @@
 """Typed configurations and the architecture registry."""
 from .base import (ConfigError, KeyReader, LayerSpec, ModelConfig, ModelSpec, PartSpec,
                    ScheduleEntry, read_config_json)
+from .banitar import BanitarConfig
 from .fiferax import FiferaxConfig
 from .gemma2 import Gemma2Config
 from .registry import (architecture_name, config_from_dict, config_from_folder,
@@ -8,9 +9,10 @@ from .registry import (architecture_name, config_from_dict, config_from_folder,
 
 register_architecture(Gemma2Config.architecture, Gemma2Config)
 register_architecture(FiferaxConfig.architecture, FiferaxConfig)
+register_architecture(BanitarConfig.architecture, BanitarConfig)
 
 __all__ = [
     "ConfigError", "KeyReader", "LayerSpec", "ModelConfig", "ModelSpec", "PartSpec", "ScheduleEntry",
-    "read_config_json", "FiferaxConfig", "Gemma2Config", "architecture_name", "config_from_dict",
+    "read_config_json", "BanitarConfig", "FiferaxConfig", "Gemma2Config", "architecture_name", "config_from_dict",
     "config_from_folder", "known_architectures", "register_architecture",
 ]

@@ -129,9 +129,14 @@ class LayerSpec:
 @dataclass
 class ScheduleEntry:
     """One run of a layer.  ``cache_from`` names an earlier entry of the
-    schedule whose cache this run reads instead of keeping one of its own."""
+    schedule whose cache this run reads instead of keeping one of its own.
+    ``enter`` names a junction of the model (an index into ``ModelSpec.junctions``)
+    that rewrites the residual stream right before this run, ``enter_index`` what
+    it is told (the number of the pass through a repeated stretch, say)."""
     layer: int
     cache_from: Optional[int] = None
+    enter: Optional[int] = None
+    enter_index: int = 0
 
 
 @dataclass
@@ -146,6 +151,7 @@ class ModelSpec:
     final_norm: PartSpec
     head: PartSpec
     stop_token_ids: list = field(default_factory=list)
+    junctions: list = field(default_factory=list)      # PartSpecs of category ``junction``
 
     def validate(self) -> None:
         if not self.layers:
@@ -153,6 +159,8 @@ class ModelSpec:
         for i, e in enumerate(self.schedule):
             if not 0 <= e.layer < len(self.layers):
                 raise ConfigError(f"schedule entry {i} names layer {e.layer} of {len(self.layers)}")
+            if e.enter is not None and not 0 <= e.enter < len(self.junctions):
+                raise ConfigError(f"schedule entry {i} enters through junction {e.enter} of {len(self.junctions)}")
             if e.cache_from is not None:
                 if not 0 <= e.cache_from < i:
                     raise ConfigError(f"schedule entry {i} reads the cache of entry {e.cache_from}, "

@@ -7,7 +7,7 @@
 // a window keeps rows modulo `ring_rows` (a multiple of AF_PAGE, >= window).
 #include "common.cuh"
 
-#define AF_MAX_HD 512
+#define AF_MAX_HD 640
 #define AF_HD_SLICES (AF_MAX_HD / 32)
 
 // ---------------------------------------------------------------- rope + cache write
@@ -291,33 +291,41 @@ AF_EXPORT int af_kv_rows(int* rows, const int* positions, const int* seq_of_toke
 // ---------------------------------------------------------------- plain attention
 
 // Online-softmax state of one (query, head) held by a warp: lane l owns the
-// elements l, l + 32, ... of the head.
+// elements l, l + 32, ... of the head.  Keys have dk elements, values dv.
 struct WarpAttn {
   float q[AF_HD_SLICES];
   float o[AF_HD_SLICES];
   float m, l;
 };
 
+// The first position that position `pos` sees.  AF_MASK_WINDOW: the last `size` positions, itself
+// included; AF_MASK_CHUNK: its own chunk of `size` positions, chunks counted from position 0.  size <= 0: all.
+__device__ __forceinline__ int first_visible(int pos, int size, int mask_kind) {
+  if (size <= 0) return 0;
+  return mask_kind == AF_MASK_CHUNK ? pos - pos % size : max(0, pos - size + 1);
+}
+
+// `sink` (or -inf): a term exp(sink) of the softmax's denominator that has no key and no value.
 template <typename T>
-__device__ __forceinline__ void attn_load_q(WarpAttn& st, const T* q, int hd, int lane) {
+__device__ __forceinline__ void attn_load_q(WarpAttn& st, const T* q, int dk, int lane, float sink = -INFINITY) {
 #pragma unroll
   for (int e = 0; e < AF_HD_SLICES; ++e) {
     const int d = lane + 32 * e;
-    st.q[e] = d < hd ? to_f32(q[d]) : 0.f;
+    st.q[e] = d < dk ? to_f32(q[d]) : 0.f;
     st.o[e] = 0.f;
   }
-  st.m = -INFINITY;
-  st.l = 0.f;
+  st.m = sink;
+  st.l = sink > -INFINITY ? 1.f : 0.f;
 }
 
 template <typename T>
-__device__ __forceinline__ void attn_key(WarpAttn& st, const T* k, const T* v, int hd, int lane,
+__device__ __forceinline__ void attn_key(WarpAttn& st, const T* k, const T* v, int dk, int dv, int lane,
                                          float scale, float cap, float bias) {
   float dot = 0.f;
 #pragma unroll
   for (int e = 0; e < AF_HD_SLICES; ++e) {
     const int d = lane + 32 * e;
-    if (d < hd) dot += st.q[e] * to_f32(k[d]);
+    if (d < dk) dot += st.q[e] * to_f32(k[d]);
   }
   dot = warp_sum(dot);
   const float s = softcap_f32(dot * scale, cap) + bias;   // bias: a position encoding's slope * (key - query)
@@ -328,30 +336,39 @@ __device__ __forceinline__ void attn_key(WarpAttn& st, const T* k, const T* v, i
 #pragma unroll
   for (int e = 0; e < AF_HD_SLICES; ++e) {
     const int d = lane + 32 * e;
-    if (d < hd) st.o[e] = st.o[e] * corr + p * to_f32(v[d]);
+    if (d < dv) st.o[e] = st.o[e] * corr + p * to_f32(v[d]);
   }
   st.m = m_new;
 }
 
+// `factor`: what the head's output is multiplied by (an output gate; 1 without one).
 template <typename T>
-__device__ __forceinline__ void attn_store(const WarpAttn& st, T* out, int hd, int lane) {
-  const float inv = st.l > 0.f ? 1.f / st.l : 0.f;
+__device__ __forceinline__ void attn_store(const WarpAttn& st, T* out, int dv, int lane, float factor = 1.f) {
+  const float inv = st.l > 0.f ? factor / st.l : 0.f;
 #pragma unroll
   for (int e = 0; e < AF_HD_SLICES; ++e) {
     const int d = lane + 32 * e;
-    if (d < hd) out[d] = from_f32<T>(st.o[e] * inv);
+    if (d < dv) out[d] = from_f32<T>(st.o[e] * inv);
   }
 }
 
+__device__ __forceinline__ float gate_factor(const float* gate, long long gate_stride, int row, int h) {
+  return gate ? 1.f / (1.f + expf(-gate[(size_t)row * gate_stride + h])) : 1.f;
+}
+
 // Prompts that start at position 0: keys and values are the step's own rows.
-// Warp w of the grid handles (token, head) = (w / nq, w % nq).
+// Warp w of the grid handles (token, head) = (w / nq, w % nq).  `hd` is the key size, `dv` the value
+// size; `sinks` (float [nq]) and `gate` (float logits, row t and column h at gate[t * gate_stride + h]:
+// the head's output is multiplied by their sigmoid) may be null.
 template <typename T>
 __global__ void attn_prefill_plain_kernel(T* __restrict__ out, int out_stride, const T* __restrict__ q,
                                           int q_stride, const T* __restrict__ k, int k_stride,
                                           const T* __restrict__ v, int v_stride,
                                           const int* __restrict__ positions,
-                                          int n_tokens, int nq, int nkv, int hd, float scale, float cap,
-                                          int window, const float* __restrict__ slopes) {
+                                          int n_tokens, int nq, int nkv, int hd, int dv, float scale, float cap,
+                                          int window, int mask_kind, const float* __restrict__ slopes,
+                                          const float* __restrict__ sinks, const float* __restrict__ gate,
+                                          long long gate_stride) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -362,25 +379,28 @@ __global__ void attn_prefill_plain_kernel(T* __restrict__ out, int out_stride, c
   const int pos = positions[t];          // position inside its sequence
   const int first_row = t - pos;         // row of the sequence's position 0
   WarpAttn st;
-  attn_load_q(st, q + (size_t)t * q_stride + (size_t)h * hd, hd, lane);
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  attn_load_q(st, q + (size_t)t * q_stride + (size_t)h * hd, hd, lane, sinks ? sinks[h] : -INFINITY);
+  const int lo = first_visible(pos, window, mask_kind);
   const float slope = slopes ? slopes[h] : 0.f;
   for (int j = lo; j <= pos; ++j) {
     const size_t r = (size_t)(first_row + j);
-    attn_key(st, k + r * k_stride + (size_t)g * hd, v + r * v_stride + (size_t)g * hd, hd, lane, scale,
+    attn_key(st, k + r * k_stride + (size_t)g * hd, v + r * v_stride + (size_t)g * dv, hd, dv, lane, scale,
              cap, slope * (float)(j - pos));
   }
-  attn_store(st, out + (size_t)t * out_stride + (size_t)h * hd, hd, lane);
+  attn_store(st, out + (size_t)t * out_stride + (size_t)h * dv, dv, lane, gate_factor(gate, gate_stride, t, h));
 }
 
 AF_EXPORT int af_attn_prefill_plain(void* out, int out_stride, const void* q, int q_stride,
                                     const void* k, int k_stride, const void* v, int v_stride, int dtype,
-                                    const int* positions, int n_tokens, int nq, int nkv, int hd,
-                                    float scale, float cap, int window, const float* slopes,
+                                    const int* positions, int n_tokens, int nq, int nkv, int hd, int dv,
+                                    float scale, float cap, int window, int mask_kind, const float* slopes,
+                                    const float* sinks, const float* gate, long long gate_stride,
                                     cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   AF_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "af_attn_prefill_plain: heads %d, groups %d", nq, nkv);
-  AF_REQUIRE(hd > 0 && hd <= AF_MAX_HD, "af_attn_prefill_plain: head_dim %d beyond %d", hd, AF_MAX_HD);
+  AF_REQUIRE(hd > 0 && hd <= AF_MAX_HD && dv > 0 && dv <= AF_MAX_HD,
+             "af_attn_prefill_plain: key size %d or value size %d beyond %d", hd, dv, AF_MAX_HD);
+  AF_REQUIRE(mask_kind == AF_MASK_WINDOW || mask_kind == AF_MASK_CHUNK, "af_attn_prefill_plain: mask kind %d", mask_kind);
   const long long warps = (long long)n_tokens * nq;
   const int wpb = 4;
   const long long blocks = (warps + wpb - 1) / wpb;
@@ -388,20 +408,23 @@ AF_EXPORT int af_attn_prefill_plain(void* out, int out_stride, const void* q, in
   AF_DISPATCH_DTYPE(dtype, T,
                     af_launch(attn_prefill_plain_kernel<T>, dim3((unsigned)blocks), dim3(wpb * 32), 0, stream, 
                         (T*)out, out_stride, (const T*)q, q_stride, (const T*)k, k_stride, (const T*)v,
-                        v_stride, positions, n_tokens, nq, nkv, hd, scale, cap, window, slopes));
+                        v_stride, positions, n_tokens, nq, nkv, hd, dv, scale, cap, window, mask_kind, slopes,
+                        sinks, gate, gate_stride));
   AF_CHECK_LAUNCH("af_attn_prefill_plain");
 }
 
 // One new token per sequence: keys and values come from the cache pages.
-// `lens[b]` counts the new token, which the cache holds already.
+// `lens[b]` counts the new token, which the cache holds already.  Key pages hold rows of `hd` elements,
+// value pages rows of `dv`; with no value pages (vcache null) a value is the first `dv` elements of its key row.
 template <typename T>
 __global__ void attn_decode_plain_kernel(T* __restrict__ out, int out_stride, const T* __restrict__ q,
                                          int q_stride, const T* __restrict__ kcache,
                                          const T* __restrict__ vcache, const int* __restrict__ page_table,
                                          int max_pages, const int* __restrict__ slots,
-                                         const int* __restrict__ lens, int batch, int nq, int nkv, int hd,
-                                         float scale, float cap, int window, int ring_rows,
-                                         const float* __restrict__ slopes) {
+                                         const int* __restrict__ lens, int batch, int nq, int nkv, int hd, int dv,
+                                         float scale, float cap, int window, int mask_kind, int ring_rows,
+                                         const float* __restrict__ slopes, const float* __restrict__ sinks,
+                                         const float* __restrict__ gate, long long gate_stride) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -410,36 +433,41 @@ __global__ void attn_decode_plain_kernel(T* __restrict__ out, int out_stride, co
   const int b = (int)(w / nq), h = (int)(w % nq);
   const int g = h / (nq / nkv);
   const int slot = slots[b];
-  T* o = out + (size_t)b * out_stride + (size_t)h * hd;
+  T* o = out + (size_t)b * out_stride + (size_t)h * dv;
   if (slot < 0) {  // padding row
-    for (int d = lane; d < hd; d += 32) o[d] = from_f32<T>(0.f);
+    for (int d = lane; d < dv; d += 32) o[d] = from_f32<T>(0.f);
     return;
   }
   const int len = lens[b];
   const int pos = len - 1;
   WarpAttn st;
-  attn_load_q(st, q + (size_t)b * q_stride + (size_t)h * hd, hd, lane);
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  attn_load_q(st, q + (size_t)b * q_stride + (size_t)h * hd, hd, lane, sinks ? sinks[h] : -INFINITY);
+  const int lo = first_visible(pos, window, mask_kind);
   const int* pt = page_table + (size_t)slot * max_pages;
   const float slope = slopes ? slopes[h] : 0.f;
   for (int j = lo; j <= pos; ++j) {
     const int r = ring_rows > 0 ? j % ring_rows : j;
     if (!AF_INDEX_OK(r / AF_PAGE < max_pages && pt[r / AF_PAGE] >= 0, r)) continue;
-    const size_t base = (((size_t)pt[r / AF_PAGE] * nkv + g) * AF_PAGE + r % AF_PAGE) * hd;
-    attn_key(st, kcache + base, vcache + base, hd, lane, scale, cap, slope * (float)(j - pos));
+    const size_t row = ((size_t)pt[r / AF_PAGE] * nkv + g) * AF_PAGE + r % AF_PAGE;
+    const T* kr = kcache + row * hd;
+    attn_key(st, kr, vcache ? vcache + row * dv : kr, hd, dv, lane, scale, cap, slope * (float)(j - pos));
   }
-  attn_store(st, o, hd, lane);
+  attn_store(st, o, dv, lane, gate_factor(gate, gate_stride, b, h));
 }
 
 AF_EXPORT int af_attn_decode_plain(void* out, int out_stride, const void* q, int q_stride,
                                    const void* kcache, const void* vcache, int dtype,
                                    const int* page_table, int max_pages, const int* slots,
-                                   const int* lens, int batch, int nq, int nkv, int hd, float scale,
-                                   float cap, int window, int ring_rows, const float* slopes,
+                                   const int* lens, int batch, int nq, int nkv, int hd, int dv, float scale,
+                                   float cap, int window, int mask_kind, int ring_rows, const float* slopes,
+                                   const float* sinks, const float* gate, long long gate_stride,
                                    cudaStream_t stream) {
   if (batch == 0) return 0;
   AF_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "af_attn_decode_plain: heads %d, groups %d", nq, nkv);
-  AF_REQUIRE(hd > 0 && hd <= AF_MAX_HD, "af_attn_decode_plain: head_dim %d beyond %d", hd, AF_MAX_HD);
+  AF_REQUIRE(hd > 0 && hd <= AF_MAX_HD && dv > 0 && dv <= AF_MAX_HD && (vcache != nullptr || dv <= hd),
+             "af_attn_decode_plain: key size %d or value size %d beyond %d (or values longer than the keys they lie in)",
+             hd, dv, AF_MAX_HD);
+  AF_REQUIRE(mask_kind == AF_MASK_WINDOW || mask_kind == AF_MASK_CHUNK, "af_attn_decode_plain: mask kind %d", mask_kind);
   AF_REQUIRE(ring_rows % AF_PAGE == 0 && (ring_rows == 0 || window > 0) && (window <= ring_rows || ring_rows == 0),
              "af_attn_decode_plain: window %d, ring rows %d", window, ring_rows);
   const long long warps = (long long)batch * nq;
@@ -448,28 +476,32 @@ AF_EXPORT int af_attn_decode_plain(void* out, int out_stride, const void* q, int
   AF_DISPATCH_DTYPE(dtype, T,
                     af_launch(attn_decode_plain_kernel<T>, dim3((unsigned)blocks), dim3(wpb * 32), 0, stream, 
                         (T*)out, out_stride, (const T*)q, q_stride, (const T*)kcache, (const T*)vcache,
-                        page_table, max_pages, slots, lens, batch, nq, nkv, hd, scale, cap, window,
-                        ring_rows, slopes));
+                        page_table, max_pages, slots, lens, batch, nq, nkv, hd, dv, scale, cap, window, mask_kind,
+                        ring_rows, slopes, sinks, gate, gate_stride));
   AF_CHECK_LAUNCH("af_attn_decode_plain");
 }
 
 // ---------------------------------------------------------------- norm + rope + cache write from a projection
 
-// Queries and keys that are normalised per head before they are rotated, and values that may be the
-// raw key projection.  The projection row of a token is float [q heads | k heads (| v heads)]; a warp per
+// Queries and keys that are normalised per head, and values that may be the raw key projection.  The
+// projection row of a token is float [q heads | k heads (| v heads of `dv` values)]; a warp per
 // (token, q or k head):
+//   x = the head's projection (+ its part of `bias`, float, laid out like the row)
 //   n = x * rsqrt(mean(x^2) + eps) * weight   (weight of head_dim values shared by the heads; none: n = x)
-//   the first rot_dim elements of n rotated by position * frequency (32-bit), the rest kept
+//   r = the first rot_dim elements of n rotated by position * frequency (32-bit), cosines and sines
+//       multiplied by `magnitude`; the rest kept
+//   with `norm_after`: r / sqrt(mean(r^2) + eps) over the whole head (no weight)
 // and written to the packed row [q | k | v] of the compute dtype; a k head also goes to its row of the
-// cache, and its value head (the raw x with `v_from_k`, else the projection's own v head) to the packed
-// row and the cache.
+// cache, and its value head (the raw x with `v_from_k`, else the projection's own v head plus its bias) to
+// the packed row and the cache.
 template <typename T>
 __global__ void __launch_bounds__(128)
 qk_norm_rope_store_kernel(T* __restrict__ qkv, long long out_stride, const float* __restrict__ proj, long long ld,
-                          const float* __restrict__ q_weight, const float* __restrict__ k_weight, float eps,
+                          const float* __restrict__ bias, const float* __restrict__ q_weight,
+                          const float* __restrict__ k_weight, float eps, int norm_after, float magnitude,
                           int v_from_k, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                           const int* __restrict__ slots, const int* __restrict__ len_after,
-                          const float* __restrict__ inv_freq, int n_tokens, int nq, int nkv, int hd, int rot_dim,
+                          const float* __restrict__ inv_freq, int n_tokens, int nq, int nkv, int hd, int dv, int rot_dim,
                           int pairing, T* __restrict__ kcache, T* __restrict__ vcache,
                           const int* __restrict__ page_table, int max_pages, int ring_rows) {
   pdl_launch_dependents();
@@ -489,46 +521,71 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, long long out_stride, const float
       if (AF_INDEX_OK(pos >= 0 && r / AF_PAGE < max_pages, r)) {
         const int page = page_table[(size_t)slot * max_pages + r / AF_PAGE];
         if (AF_INDEX_OK(page >= 0, page)) {
-          const size_t at = (((size_t)page * nkv + (head - nq)) * AF_PAGE + r % AF_PAGE) * hd;
-          kdst = kcache + at;
-          vdst = vcache + at;
+          const size_t at = ((size_t)page * nkv + (head - nq)) * AF_PAGE + r % AF_PAGE;
+          kdst = kcache + at * hd;
+          vdst = vcache + at * dv;
         }
       }
     }
   }
   pdl_wait();
   const float* x = proj + (size_t)t * ld + (size_t)head * hd;
+  const float* xb = bias ? bias + (size_t)head * hd : nullptr;
   const float* w = is_k ? k_weight : q_weight;
   T* orow = qkv + (size_t)t * out_stride;
   T* dst = orow + (size_t)head * hd;                        // q heads and k heads keep their places
   float inv = 1.f;
   if (w != nullptr) {
     float ss = 0.f;
-    for (int i = lane; i < hd; i += 32) ss += x[i] * x[i];
+    for (int i = lane; i < hd; i += 32) {
+      const float v = x[i] + (xb ? xb[i] : 0.f);
+      ss += v * v;
+    }
     ss = warp_sum(ss);
     inv = rsqrtf(ss / (float)hd + eps);
+  }
+  float after = 1.f;
+  if (norm_after) {
+    // a rotation keeps a pair's length: the mean square after it is that of the rotated elements times
+    // magnitude^2 plus that of the others
+    float lo = 0.f, hi = 0.f;
+    for (int i = lane; i < hd; i += 32) {
+      float v = x[i] + (xb ? xb[i] : 0.f);
+      if (w) v *= inv * w[i];
+      if (i < rot_dim) lo += v * v; else hi += v * v;
+    }
+    lo = warp_sum(lo);
+    hi = warp_sum(hi);
+    after = rsqrtf((magnitude * magnitude * lo + hi) / (float)hd + eps);
   }
   const int half = rot_dim / 2;
   for (int p = lane; p < half; p += 32) {
     const int i0 = pairing == AF_PAIR_HALF ? p : 2 * p;
     const int i1 = pairing == AF_PAIR_HALF ? p + half : 2 * p + 1;
-    const float a = w ? x[i0] * inv * w[i0] : x[i0], b = w ? x[i1] * inv * w[i1] : x[i1];
+    float a = x[i0] + (xb ? xb[i0] : 0.f), b = x[i1] + (xb ? xb[i1] : 0.f);
+    if (w) a *= inv * w[i0], b *= inv * w[i1];
     float s, c;
     sincosf((float)pos * inv_freq[p], &s, &c);
-    const T ra = from_f32<T>(a * c - b * s), rb = from_f32<T>(b * c + a * s);
+    s *= magnitude, c *= magnitude;
+    const T ra = from_f32<T>((a * c - b * s) * after), rb = from_f32<T>((b * c + a * s) * after);
     dst[i0] = ra, dst[i1] = rb;
     if (kdst != nullptr) kdst[i0] = ra, kdst[i1] = rb;
   }
   for (int i = rot_dim + lane; i < hd; i += 32) {
-    const T v = from_f32<T>(w ? x[i] * inv * w[i] : x[i]);
+    float a = x[i] + (xb ? xb[i] : 0.f);
+    if (w) a *= inv * w[i];
+    const T v = from_f32<T>(a * after);
     dst[i] = v;
     if (kdst != nullptr) kdst[i] = v;
   }
   if (is_k) {
-    const float* vx = v_from_k ? x : proj + (size_t)t * ld + (size_t)(head + nkv) * hd;
-    T* vrow = orow + (size_t)(head + nkv) * hd;
-    for (int i = lane; i < hd; i += 32) {
-      const T v = from_f32<T>(vx[i]);
+    const int g = head - nq;
+    const size_t v_off = (size_t)(nq + nkv) * hd + (size_t)g * dv;          // the value head's place, in both rows
+    const float* vx = v_from_k ? x : proj + (size_t)t * ld + v_off;
+    const float* vb = bias == nullptr ? nullptr : (v_from_k ? xb : bias + v_off);
+    T* vrow = orow + v_off;
+    for (int i = lane; i < dv; i += 32) {
+      const T v = from_f32<T>(vx[i] + (vb && !v_from_k ? vb[i] : 0.f));
       vrow[i] = v;
       if (vdst != nullptr) vdst[i] = v;
     }
@@ -536,13 +593,15 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, long long out_stride, const float
 }
 
 AF_EXPORT int af_qk_norm_rope_store(void* qkv, int dtype, long long out_stride, const float* proj, long long ld,
-                                    const float* q_weight, const float* k_weight, float eps, int v_from_k,
+                                    const float* bias, const float* q_weight, const float* k_weight, float eps,
+                                    int norm_after, float magnitude, int v_from_k,
                                     const int* positions, const int* seq_of_token, const int* slots,
                                     const int* len_after, const float* inv_freq, int n_tokens, int nq, int nkv, int hd,
-                                    int rot_dim, int pairing, void* kcache, void* vcache, const int* page_table,
+                                    int dv, int rot_dim, int pairing, void* kcache, void* vcache, const int* page_table,
                                     int max_pages, int ring_rows, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
-  AF_REQUIRE(n_tokens > 0 && nq > 0 && nkv > 0 && hd > 0, "af_qk_norm_rope_store: bad sizes");
+  AF_REQUIRE(n_tokens > 0 && nq > 0 && nkv > 0 && hd > 0 && dv > 0, "af_qk_norm_rope_store: bad sizes");
+  AF_REQUIRE(!v_from_k || dv == hd, "af_qk_norm_rope_store: values that are the keys have their size");
   AF_REQUIRE(rot_dim >= 0 && rot_dim <= hd && rot_dim % 2 == 0,
              "af_qk_norm_rope_store: rotary dim %d must be even and <= head_dim %d", rot_dim, hd);
   AF_REQUIRE(pairing == AF_PAIR_HALF || pairing == AF_PAIR_ADJACENT, "af_qk_norm_rope_store: pairing");
@@ -554,8 +613,134 @@ AF_EXPORT int af_qk_norm_rope_store(void* qkv, int dtype, long long out_stride, 
   AF_REQUIRE(blocks < (1ll << 31), "af_qk_norm_rope_store: too many rows");
   AF_DISPATCH_DTYPE(dtype, T,
                     af_launch(qk_norm_rope_store_kernel<T>, dim3((unsigned)blocks), dim3(128), 0, stream, (T*)qkv,
-                              out_stride, proj, ld, q_weight, k_weight, eps, v_from_k, positions, seq_of_token, slots,
-                              len_after, inv_freq, n_tokens, nq, nkv, hd, rot_dim, pairing, (T*)kcache, (T*)vcache,
-                              page_table, max_pages, ring_rows));
+                              out_stride, proj, ld, bias, q_weight, k_weight, eps, norm_after, magnitude, v_from_k,
+                              positions, seq_of_token, slots, len_after, inv_freq, n_tokens, nq, nkv, hd, dv, rot_dim,
+                              pairing, (T*)kcache, (T*)vcache, page_table, max_pages, ring_rows));
   AF_CHECK_LAUNCH("af_qk_norm_rope_store");
+}
+
+// ---------------------------------------------------------------- keys and values from a latent vector
+
+// From float projection rows [q heads of (dim + rot) | latent of `rank` | shared key part of `rot`]:
+//   q heads: the last `rot` elements of every head rotated (pairs i, i + rot / 2), the first `dim` kept,
+//            into the rows `q` [heads * (dim + rot)] of the compute dtype;
+//   the latent divided by its root mean square (eps inside the root) times `norm_w`, and the shared key
+//   part rotated, into the row `kv` [rank + rot] of the compute dtype and into the token's row of its cache
+//   page (one kv head of rank + rot elements; the values are the latent part of the same row).
+// One block per token.
+template <typename T>
+__global__ void __launch_bounds__(128)
+latent_prep_kernel(T* __restrict__ q, long long q_stride, T* __restrict__ kv, long long kv_stride,
+                   const float* __restrict__ proj, long long ld, const float* __restrict__ norm_w, float eps,
+                   const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                   const int* __restrict__ slots, const int* __restrict__ len_after,
+                   const float* __restrict__ inv_freq, int heads, int dim, int rot, int rank,
+                   T* __restrict__ kcache, const int* __restrict__ page_table, int max_pages, int ring_rows) {
+  pdl_launch_dependents();
+  __shared__ float scratch[33];
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int width = rank + rot;
+  T* kdst = nullptr;
+  if (kcache != nullptr) {
+    const int seq = seq_of_token[t];
+    const int slot = slots[seq];
+    if (slot >= 0 && !(ring_rows > 0 && pos + ring_rows < len_after[seq])) {
+      const int r = ring_rows > 0 ? pos % ring_rows : pos;
+      if (AF_INDEX_OK(pos >= 0 && r / AF_PAGE < max_pages, r)) {
+        const int page = page_table[(size_t)slot * max_pages + r / AF_PAGE];
+        if (AF_INDEX_OK(page >= 0, page)) kdst = kcache + ((size_t)page * AF_PAGE + r % AF_PAGE) * width;
+      }
+    }
+  }
+  pdl_wait();
+  const float* x = proj + (size_t)t * ld;
+  const float* lat = x + (size_t)heads * (dim + rot);
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < rank; i += blockDim.x) ss += lat[i] * lat[i];
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)rank + eps);
+  T* kvr = kv + (size_t)t * kv_stride;
+  for (int i = threadIdx.x; i < rank; i += blockDim.x) {
+    const T v = from_f32<T>(lat[i] * inv * norm_w[i]);
+    kvr[i] = v;
+    if (kdst != nullptr) kdst[i] = v;
+  }
+  const int half = rot / 2;
+  T* qr = q + (size_t)t * q_stride;
+  // rotated pairs: unit heads + 1 is the shared key part
+  for (int i = threadIdx.x; i < (heads + 1) * half; i += blockDim.x) {
+    const int u = i / half, p = i - u * half;
+    float s, c;
+    sincosf((float)pos * inv_freq[p], &s, &c);
+    const float* src = u < heads ? x + (size_t)u * (dim + rot) + dim : lat + rank;
+    const float a = src[p], b = src[p + half];
+    const T ra = from_f32<T>(a * c - b * s), rb = from_f32<T>(b * c + a * s);
+    if (u < heads) {
+      T* d = qr + (size_t)u * (dim + rot) + dim;
+      d[p] = ra, d[p + half] = rb;
+    } else {
+      kvr[rank + p] = ra, kvr[rank + p + half] = rb;
+      if (kdst != nullptr) kdst[rank + p] = ra, kdst[rank + p + half] = rb;
+    }
+  }
+  for (int i = threadIdx.x; i < heads * dim; i += blockDim.x) {
+    const int u = i / dim, e = i - u * dim;
+    qr[(size_t)u * (dim + rot) + e] = from_f32<T>(x[(size_t)u * (dim + rot) + e]);
+  }
+}
+
+AF_EXPORT int af_latent_prep(void* q, long long q_stride, void* kv, long long kv_stride, int dtype, const float* proj,
+                             long long ld, const float* norm_w, float eps, const int* positions,
+                             const int* seq_of_token, const int* slots, const int* len_after, const float* inv_freq,
+                             int n_tokens, int heads, int dim, int rot, int rank, void* kcache, const int* page_table,
+                             int max_pages, int ring_rows, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  AF_REQUIRE(n_tokens > 0 && heads > 0 && dim >= 0 && rot >= 0 && rot % 2 == 0 && rank > 0 && dim + rot > 0,
+             "af_latent_prep: bad sizes");
+  AF_REQUIRE(ring_rows % AF_PAGE == 0, "af_latent_prep: ring rows %d not whole pages", ring_rows);
+  AF_DISPATCH_DTYPE(dtype, T,
+                    af_launch(latent_prep_kernel<T>, dim3(n_tokens), dim3(128), 0, stream, (T*)q, q_stride, (T*)kv,
+                              kv_stride, proj, ld, norm_w, eps, positions, seq_of_token, slots, len_after, inv_freq,
+                              heads, dim, rot, rank, (T*)kcache, page_table, max_pages, ring_rows));
+  AF_CHECK_LAUNCH("af_latent_prep");
+}
+
+// ---------------------------------------------------------------- a small product per head
+
+// out[t, h, n] = sum_d x[t, h, d] * w[h, d, n] for d < D, n < N (32-bit sums in index order), and the
+// `extra` elements that follow a head's D inputs copied behind its N outputs.  x rows: heads of
+// (D + extra) elements, `x_stride` apart; out rows: heads of (N + extra), `out_stride` apart; w [heads, D, N].
+// One block per (token, head); the head's inputs wait in shared memory.
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_project_kernel(T* __restrict__ out, long long out_stride, const T* __restrict__ x, long long x_stride,
+                    const T* __restrict__ w, int D, int N, int extra) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float xs[];
+  const int t = blockIdx.x, h = blockIdx.y;
+  const T* xr = x + (size_t)t * x_stride + (size_t)h * (D + extra);
+  T* o = out + (size_t)t * out_stride + (size_t)h * (N + extra);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) xs[d] = to_f32(xr[d]);
+  for (int e = threadIdx.x; e < extra; e += blockDim.x) o[N + e] = xr[D + e];
+  __syncthreads();
+  const T* wh = w + (size_t)h * D * N;
+  for (int n = threadIdx.x; n < N; n += blockDim.x) {
+    float acc = 0.f;
+    for (int d = 0; d < D; ++d) acc += xs[d] * to_f32(wh[(size_t)d * N + n]);
+    o[n] = from_f32<T>(acc);
+  }
+}
+
+AF_EXPORT int af_head_project(void* out, long long out_stride, const void* x, long long x_stride, const void* w,
+                              int dtype, int n_tokens, int heads, int D, int N, int extra, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  AF_REQUIRE(n_tokens > 0 && heads > 0 && heads < 65536 && D > 0 && N > 0 && extra >= 0, "af_head_project: bad sizes");
+  AF_REQUIRE((size_t)D * sizeof(float) <= 48 * 1024, "af_head_project: %d inputs a head beyond 12288", D);
+  const int threads = N >= 256 ? 256 : ((N + 31) / 32) * 32;
+  AF_DISPATCH_DTYPE(dtype, T,
+                    af_launch(head_project_kernel<T>, dim3(n_tokens, heads), dim3(threads), (size_t)D * sizeof(float),
+                              stream, (T*)out, out_stride, (const T*)x, x_stride, (const T*)w, D, N, extra));
+  AF_CHECK_LAUNCH("af_head_project");
 }

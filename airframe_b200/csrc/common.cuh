@@ -17,6 +17,10 @@ enum AfAct { AF_ACT_GELU_TANH = 0, AF_ACT_SILU = 1 };
 // rotary pairings
 enum AfPairing { AF_PAIR_HALF = 0, AF_PAIR_ADJACENT = 1 };
 
+// which earlier positions a position sees: the last `size` ones (a sliding window), or those of its own
+// chunk of `size` positions
+enum AfMask { AF_MASK_WINDOW = 0, AF_MASK_CHUNK = 1 };
+
 // The fused arg-max keeps one 64-bit key per token; keys lie this many words apart (a cache line each:
 // every block of the head joins its best into every token's key, and keys in one line would queue up
 // behind one another in the L2).

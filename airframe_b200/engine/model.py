@@ -32,6 +32,7 @@ class Model:
         self.ctx = BuildContext(compute_dtype=compute_dtype, device=torch.device(device))
         self.embedding = build_part("embedding", spec.embedding, self.ctx)
         self.blocks = _build_layers(spec, self.ctx)
+        self.junctions = [build_part("junction", j, self.ctx) for j in spec.junctions]
         self.final_norm = build_part("norm", spec.final_norm, self.ctx)
         self.head = build_part("head", spec.head, self.ctx)
         self.loaded = False
@@ -39,7 +40,7 @@ class Model:
     # ------------------------------------------------------------------ weights
 
     def parts(self):
-        return [self.embedding, *self.blocks, self.final_norm, self.head]
+        return [self.embedding, *self.blocks, *self.junctions, self.final_norm, self.head]
 
     def weight_decls(self) -> list:
         seen, out = set(), []
@@ -82,11 +83,13 @@ class Model:
         every weight it uses once and the cache of the live sequences (the parts
         answer for themselves; a run that reads another run's cache reads it again)."""
         total = self.embedding.decode_bytes(lens) + self.final_norm.decode_bytes(lens) + self.head.decode_bytes(lens)
+        total += sum(self.junctions[e.enter].decode_bytes(lens) for e in self.spec.schedule if e.enter is not None)
         return total + sum(self.blocks[e.layer].decode_bytes(lens) for e in self.spec.schedule)
 
     def prefill_flops(self, lens, n_logits: int) -> int:
         """Floating-point operations of a prefill of prompts of ``lens`` tokens with ``n_logits`` rows of logits."""
         total = sum(self.blocks[e.layer].prefill_flops(lens) for e in self.spec.schedule)
+        total += sum(self.junctions[e.enter].prefill_flops(lens) for e in self.spec.schedule if e.enter is not None)
         flops = getattr(self.head, "logits_flops", None)
         return total + (flops(n_logits) if flops is not None else 0)
 
@@ -109,10 +112,18 @@ class Model:
         if probe is not None:
             probe.after(-1, -1, x, batch)
         sched = self.spec.schedule
+        # a junction sees the embedding's output beside the stream (which the layers rewrite in place)
+        x0 = x.clone() if any(e.enter is not None for e in sched) else None
         normed = None
         for i, e in enumerate(sched):
             blk = self.blocks[e.layer]
-            nxt = self.blocks[sched[i + 1].layer].first_norm() if i + 1 < len(sched) else None
+            if e.enter is not None:
+                normed = self.junctions[e.enter].forward(x, x0, e.enter_index, batch, then=blk.first_norm(),
+                                                         out_dtype=self.ctx.compute_dtype)
+            # the last kernel of a run also makes the next run's first norm, unless a junction rewrites the stream first
+            nxt = None
+            if i + 1 < len(sched) and sched[i + 1].enter is None:
+                nxt = self.blocks[sched[i + 1].layer].first_norm()
             normed = blk.forward(x, batch, cache.views[i], normed=normed, next_pre=nxt)
             if probe is not None:
                 probe.after(i, e.layer, x, batch)

@@ -18,6 +18,7 @@ from .kernels_const import PAGE
 F32, BF16 = 0, 1
 ACTIVATIONS = {"gelu_tanh": 0, "silu": 1}
 PAIRINGS = {"half": 0, "adjacent": 1}
+MASKS = {"window": 0, "chunk": 1}      # the last `size` positions / the position's own chunk of `size`
 
 
 class KernelError(RuntimeError):
@@ -258,37 +259,67 @@ def sum_parts(qkv, parts, batch, nq: int, nkv: int, hd: int) -> None:
     rope_cache_write(qkv, batch.positions, _no_frequencies(qkv.device), nq, nkv, hd, 0, "half", parts=parts)
 
 
+def _gate_args(gate, rows: int, nq: int, who: str):
+    """Pointer and row stride of per-head gate logits (float32, row t and head h at [t, h]; columns may be
+    a slice of wider rows)."""
+    if gate is None:
+        return c_void_p(0), c_longlong(0)
+    if gate.dtype != torch.float32 or gate.dim() != 2 or gate.shape[0] != rows or gate.shape[1] != nq or gate.stride(1) != 1:
+        raise KernelError(f"{who}: gate logits must be float32 [{rows}, {nq}] with unit column stride")
+    return _ptr(gate, "gate", torch.float32), c_longlong(gate.stride(0))
+
+
 def attn_prefill_plain(out, q, k, v, positions, nq: int, nkv: int, hd: int, scale: float, cap: float,
-                       window: int, slopes=None) -> None:
+                       window: int, slopes=None, dv=None, mask: str = "window", sinks=None, gate=None) -> None:
     """Attention of prompts that start at position 0 over the step's own keys.
-    q [T, nq*hd], k/v [T, nkv*hd] are row views (any row stride).  ``slopes``
-    (float32 [nq]): slope[h] * (key position - query position) is added to head
-    h's scores after scale and cap (a position encoding that biases scores)."""
+    q [T, nq*hd], k [T, nkv*hd], v [T, nkv*dv] are row views (any row stride; ``dv`` = hd by default).
+    ``window`` > 0 with ``mask`` "window": a position sees the last ``window`` ones; "chunk": those of its
+    own chunk of ``window`` positions.  ``slopes`` (float32 [nq]): slope[h] * (key position - query position)
+    is added to head h's scores after scale and cap (a position encoding that biases scores).  ``sinks``
+    (float32 [nq]): exp(sink[h]) joins head h's softmax denominator without a key or a value.  ``gate``
+    (float32 [T, nq] logits): head h's output is multiplied by their sigmoid."""
     if slopes is not None and slopes.numel() != nq:
         raise KernelError(f"attn_prefill_plain: {slopes.numel()} slopes for {nq} heads")
+    if sinks is not None and sinks.numel() != nq:
+        raise KernelError(f"attn_prefill_plain: {sinks.numel()} sinks for {nq} heads")
+    if mask not in MASKS:
+        raise KernelError(f"attn_prefill_plain: unknown mask '{mask}'")
     T = q.shape[0]
+    gp, gs = _gate_args(gate, T, nq, "attn_prefill_plain")
     _check(_lib().af_attn_prefill_plain(
         _ptr(out), c_int(_rows(out, "out")), _ptr(q), c_int(_rows(q, "q")), _ptr(k), c_int(_rows(k, "k")),
         _ptr(v), c_int(_rows(v, "v")), c_int(dtype_code(q.dtype)), _ptr(positions, "positions", torch.int32),
-        c_int(T), c_int(nq), c_int(nkv), c_int(hd), c_float(scale), c_float(cap), c_int(window),
-        _ptr(slopes, "slopes", torch.float32, allow_none=True), _stream()))
+        c_int(T), c_int(nq), c_int(nkv), c_int(hd), c_int(dv or hd), c_float(scale), c_float(cap), c_int(window),
+        c_int(MASKS[mask]), _ptr(slopes, "slopes", torch.float32, allow_none=True),
+        _ptr(sinks, "sinks", torch.float32, allow_none=True), gp, gs, _stream()))
 
 
 def attn_decode_plain(out, q, kcache, vcache, page_table, slots, lens, nq: int, nkv: int, hd: int,
-                      scale: float, cap: float, window: int, ring_rows: int, slopes=None) -> None:
-    """Attention of one new token per sequence over the cache pages
-    (``slopes`` as in :func:`attn_prefill_plain`)."""
+                      scale: float, cap: float, window: int, ring_rows: int, slopes=None, dv=None,
+                      mask: str = "window", sinks=None, gate=None) -> None:
+    """Attention of one new token per sequence over the cache pages (options as in
+    :func:`attn_prefill_plain`).  ``vcache`` None: a value is the first ``dv`` elements of its key row."""
     B = q.shape[0]
     if slopes is not None and slopes.numel() != nq:
         raise KernelError(f"attn_decode_plain: {slopes.numel()} slopes for {nq} heads")
+    if sinks is not None and sinks.numel() != nq:
+        raise KernelError(f"attn_decode_plain: {sinks.numel()} sinks for {nq} heads")
+    if mask not in MASKS:
+        raise KernelError(f"attn_decode_plain: unknown mask '{mask}'")
     if kcache.dtype != q.dtype:
         raise KernelError("attn_decode_plain: cache dtype differs from the activations'")
+    dv = dv or hd
+    if tuple(kcache.shape[1:]) != (nkv, PAGE, hd) or (vcache is not None and tuple(vcache.shape[1:]) != (nkv, PAGE, dv)):
+        raise KernelError(f"attn_decode_plain: cache pages must be [pages, {nkv}, {PAGE}, {hd}] (values {dv})")
+    gp, gs = _gate_args(gate, B, nq, "attn_decode_plain")
     _check(_lib().af_attn_decode_plain(
-        _ptr(out), c_int(_rows(out, "out")), _ptr(q), c_int(_rows(q, "q")), _ptr(kcache), _ptr(vcache),
+        _ptr(out), c_int(_rows(out, "out")), _ptr(q), c_int(_rows(q, "q")), _ptr(kcache),
+        _ptr(vcache, allow_none=True),
         c_int(dtype_code(q.dtype)), _ptr(page_table, "page_table", torch.int32), c_int(page_table.shape[1]),
         _ptr(slots, "slots", torch.int32), _ptr(lens, "lens", torch.int32), c_int(B), c_int(nq), c_int(nkv),
-        c_int(hd), c_float(scale), c_float(cap), c_int(window), c_int(ring_rows),
-        _ptr(slopes, "slopes", torch.float32, allow_none=True), _stream()))
+        c_int(hd), c_int(dv), c_float(scale), c_float(cap), c_int(window), c_int(MASKS[mask]), c_int(ring_rows),
+        _ptr(slopes, "slopes", torch.float32, allow_none=True), _ptr(sinks, "sinks", torch.float32, allow_none=True),
+        gp, gs, _stream()))
 
 
 def add_(x, a) -> None:
@@ -587,12 +618,16 @@ def attn_prefill_tc(out, q, k, v, seq_starts, n_seqs: int, max_len: int, nq, nkv
         c_float(cap), c_int(window), _ptr(error_word(q.device), "err", torch.int32), _stream()))
 
 
-def attn_prefill(out, q, k, v, batch, nq, nkv, hd, scale, cap, window, slopes=None) -> None:
+def attn_prefill(out, q, k, v, batch, nq, nkv, hd, scale, cap, window, slopes=None, dv=None, mask: str = "window",
+                 sinks=None, gate=None) -> None:
     """Attention of a prefill step: for bfloat16 the tcgen05 kernel (head sizes
     128, 256) or the mma.sync kernel (64), else the plain kernel (which also
-    serves scores with a per-head slope)."""
-    if slopes is not None:
-        attn_prefill_plain(out, q, k, v, batch.positions, nq, nkv, hd, scale, cap, window, slopes)
+    serves scores with a per-head slope, values of another size than the keys, sinks and gates)."""
+    special = (slopes is not None or (dv or hd) != hd or sinks is not None or gate is not None
+               or (mask != "window" and window))
+    if special:
+        attn_prefill_plain(out, q, k, v, batch.positions, nq, nkv, hd, scale, cap, window, slopes, dv=dv, mask=mask,
+                           sinks=sinks, gate=gate)
         return
     aligned = all(t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0 for t in (q, k, v, out))
     if q.dtype == torch.bfloat16 and aligned and _lib().af_attn_prefill_tc_supported(c_int(hd)):
@@ -667,11 +702,14 @@ def attn_decode_split(out, q, kcache, vcache, page_table, slots, lens, nq, nkv, 
 ATTN_DECODE_MAX_SEQS = 2048     # sequences of a step that the split kernel plans for (more: the plain kernel)
 
 
-def attn_decode(out, q, kv, batch, nq, nkv, hd, scale, cap, window, slopes=None) -> None:
+def attn_decode(out, q, kv, batch, nq, nkv, hd, scale, cap, window, slopes=None, dv=None, mask: str = "window",
+                sinks=None, gate=None) -> None:
     """Attention of a decode step over the cache: the split kernel for
     bfloat16 and head sizes it takes, else the plain kernel (which also serves
-    scores with a per-head slope)."""
-    if (slopes is None and q.dtype == torch.bfloat16 and _lib().af_attn_decode_supported(c_int(hd))
+    scores with a per-head slope, values of another size than the keys or inside them, sinks and gates)."""
+    special = (slopes is not None or (dv or hd) != hd or kv.v is None or sinks is not None or gate is not None
+               or (mask != "window" and window))
+    if (not special and q.dtype == torch.bfloat16 and _lib().af_attn_decode_supported(c_int(hd))
             and batch.n_seqs <= ATTN_DECODE_MAX_SEQS):
         n = attn_decode_max_splits(batch.n_seqs, nkv, batch.max_len_after, window, nq=nq)
         # the plan of the step, shared by the layers that read this group of caches alike (a batch without a
@@ -687,7 +725,7 @@ def attn_decode(out, q, kv, batch, nq, nkv, hd, scale, cap, window, slopes=None)
                           window, kv.ring_rows, n, plan=plan)
         return
     attn_decode_plain(out, q, kv.k, kv.v, kv.page_table, batch.slots, batch.len_after, nq, nkv, hd,
-                      scale, cap, window, kv.ring_rows, slopes)
+                      scale, cap, window, kv.ring_rows, slopes, dv=dv, mask=mask, sinks=sinks, gate=gate)
 
 
 # ---------------------------------------------------------------- mixers with a state of fixed size
@@ -794,39 +832,144 @@ def gated_scan(y, proj, off_z: int, off_x: int, off_g: int, bz, bx, state, batch
 
 
 def qk_norm_rope_store(qkv, proj, batch, nq: int, nkv: int, hd: int, inv_freq, rot_dim: int, pairing: str,
-                       q_weight=None, k_weight=None, eps: float = 0.0, v_from_k: bool = False, kv=None) -> None:
-    """From float32 projection rows [q heads | k heads (| v heads)]: q and k heads normalised per head
+                       q_weight=None, k_weight=None, eps: float = 0.0, v_from_k: bool = False, kv=None,
+                       bias=None, norm_after: bool = False, magnitude: float = 1.0, dv=None) -> None:
+    """From float32 projection rows [q heads | k heads (| v heads of ``dv`` values)], plus ``bias`` (float32,
+    laid out like a row) when given: q and k heads normalised per head
     (x * rsqrt(mean x^2 + eps) * weight, the weight of ``hd`` values shared by the heads; no weights: as
-    they are), their first ``rot_dim`` elements rotated, into the packed rows ``qkv`` [q | k | v] of the
+    they are), their first ``rot_dim`` elements rotated (cosines and sines times ``magnitude``), with
+    ``norm_after`` divided by their root mean square over the head after that (eps inside the root, no weight),
+    into the packed rows ``qkv`` [q | k | v] of the
     compute dtype; the value heads are the raw k heads of the projection (``v_from_k``) or the projection's own.
     With ``kv`` (the layer's view of its cache pages) k and v also go to each token's row of its page."""
     T = proj.shape[0]
-    width_in = (nq + nkv) * hd if v_from_k else (nq + 2 * nkv) * hd
-    if proj.shape[1] < width_in or tuple(qkv.shape) != (T, (nq + 2 * nkv) * hd):
-        raise KernelError(f"qk_norm_rope_store: projection of {width_in} columns into rows of {(nq + 2 * nkv) * hd}")
+    dv = dv or hd
+    width_in = (nq + nkv) * hd if v_from_k else (nq + nkv) * hd + nkv * dv
+    if proj.shape[1] < width_in or tuple(qkv.shape) != (T, (nq + nkv) * hd + nkv * dv):
+        raise KernelError(f"qk_norm_rope_store: projection of {width_in} columns into rows of {(nq + nkv) * hd + nkv * dv}")
     if pairing not in PAIRINGS or inv_freq.numel() != rot_dim // 2:
         raise KernelError("qk_norm_rope_store: pairing, or inv_freq does not hold rot_dim / 2 values")
     for wgt in (q_weight, k_weight):
         if wgt is not None and wgt.numel() != hd:
             raise KernelError(f"qk_norm_rope_store: a norm weight of {hd} values")
+    if bias is not None and bias.numel() < width_in:
+        raise KernelError(f"qk_norm_rope_store: a bias of {width_in} values")
     kc = vc = pt = None
     max_pages = ring = 0
     if kv is not None:
         kc, vc, pt, ring = kv.k, kv.v, kv.page_table, kv.ring_rows
-        if kc.dtype != qkv.dtype or tuple(kc.shape[1:]) != (nkv, PAGE, hd) or not kc.is_contiguous() \
-                or not vc.is_contiguous():
-            raise KernelError(f"qk_norm_rope_store: cache pages must be [pages, {nkv}, {PAGE}, {hd}] of the rows' dtype")
+        if kc.dtype != qkv.dtype or tuple(kc.shape[1:]) != (nkv, PAGE, hd) or vc is None \
+                or tuple(vc.shape[1:]) != (nkv, PAGE, dv) or not kc.is_contiguous() or not vc.is_contiguous():
+            raise KernelError(f"qk_norm_rope_store: cache pages must be [pages, {nkv}, {PAGE}, {hd}] (values {dv}) "
+                              "of the rows' dtype")
         max_pages = pt.shape[1]
     pp, ld = _f32_rows(proj, "proj")
     _check(_lib().af_qk_norm_rope_store(
         _ptr(qkv), c_int(dtype_code(qkv.dtype)), c_longlong(_rows(qkv, "qkv")), pp, ld,
+        _ptr(bias, "bias", torch.float32, allow_none=True),
         _ptr(q_weight, "q_weight", torch.float32, allow_none=True),
-        _ptr(k_weight, "k_weight", torch.float32, allow_none=True), c_float(eps), c_int(1 if v_from_k else 0),
+        _ptr(k_weight, "k_weight", torch.float32, allow_none=True), c_float(eps), c_int(1 if norm_after else 0),
+        c_float(magnitude), c_int(1 if v_from_k else 0),
         _ptr(batch.positions, "positions", torch.int32), _ptr(batch.seq_of_token, "seq_of_token", torch.int32),
         _ptr(batch.slots, "slots", torch.int32), _ptr(batch.len_after, "len_after", torch.int32),
-        _ptr(inv_freq, "inv_freq", torch.float32), c_int(T), c_int(nq), c_int(nkv), c_int(hd), c_int(rot_dim),
+        _ptr(inv_freq, "inv_freq", torch.float32), c_int(T), c_int(nq), c_int(nkv), c_int(hd), c_int(dv), c_int(rot_dim),
         c_int(PAIRINGS[pairing]), _ptr(kc, allow_none=True), _ptr(vc, allow_none=True),
         _ptr(pt, "page_table", torch.int32, allow_none=True), c_int(max_pages), c_int(ring), _stream()))
+
+
+def latent_prep(q, kvrow, proj, batch, heads: int, dim: int, rot: int, rank: int, norm_w, eps: float, inv_freq,
+                kv=None) -> None:
+    """From float32 projection rows [q heads of (dim + rot) | latent of ``rank`` | shared key part of ``rot``]:
+    the q heads with their last ``rot`` elements rotated (pairs i, i + rot / 2) into ``q`` [T, heads (dim + rot)];
+    the latent over its root mean square (eps inside the root) times ``norm_w`` and the rotated shared key part
+    into ``kvrow`` [T, rank + rot], and, with ``kv`` (the layer's view of its cache: one kv head of rank + rot
+    elements, no value pages), into each token's row of its page."""
+    T = proj.shape[0]
+    if proj.shape[1] < heads * (dim + rot) + rank + rot or tuple(q.shape) != (T, heads * (dim + rot)) \
+            or tuple(kvrow.shape) != (T, rank + rot) or q.dtype != kvrow.dtype:
+        raise KernelError("latent_prep: shapes of the projection, q and kv rows do not fit")
+    if inv_freq.numel() != rot // 2 or norm_w.numel() != rank:
+        raise KernelError("latent_prep: inv_freq holds rot / 2 values, the norm weight rank values")
+    kc = pt = None
+    max_pages = ring = 0
+    if kv is not None:
+        kc, pt, ring = kv.k, kv.page_table, kv.ring_rows
+        if kc.dtype != q.dtype or tuple(kc.shape[1:]) != (1, PAGE, rank + rot) or not kc.is_contiguous():
+            raise KernelError(f"latent_prep: cache pages must be [pages, 1, {PAGE}, {rank + rot}] of the rows' dtype")
+        max_pages = pt.shape[1]
+    pp, ld = _f32_rows(proj, "proj")
+    _check(_lib().af_latent_prep(
+        _ptr(q), c_longlong(_rows(q, "q")), _ptr(kvrow), c_longlong(_rows(kvrow, "kvrow")), c_int(dtype_code(q.dtype)),
+        pp, ld, _ptr(norm_w, "norm_w", torch.float32), c_float(eps), _ptr(batch.positions, "positions", torch.int32),
+        _ptr(batch.seq_of_token, "seq_of_token", torch.int32), _ptr(batch.slots, "slots", torch.int32),
+        _ptr(batch.len_after, "len_after", torch.int32), _ptr(inv_freq, "inv_freq", torch.float32), c_int(T),
+        c_int(heads), c_int(dim), c_int(rot), c_int(rank), _ptr(kc, allow_none=True),
+        _ptr(pt, "page_table", torch.int32, allow_none=True), c_int(max_pages), c_int(ring), _stream()))
+
+
+def head_project(out, x, w, heads: int, D: int, N: int, extra: int = 0) -> None:
+    """out[t, h, :N] = x[t, h, :D] @ w[h] for w [heads, D, N] (32-bit sums), and the ``extra`` elements behind a
+    head's D inputs copied behind its N outputs.  x [T, heads (D + extra)], out [T, heads (N + extra)]: row views
+    of one dtype, which is w's too."""
+    T = x.shape[0]
+    if tuple(x.shape) != (T, heads * (D + extra)) or tuple(out.shape) != (T, heads * (N + extra)) \
+            or tuple(w.shape) != (heads, D, N) or not w.is_contiguous() or not (x.dtype == out.dtype == w.dtype):
+        raise KernelError("head_project: shapes or dtypes do not fit")
+    _check(_lib().af_head_project(_ptr(out), c_longlong(_rows(out, "out")), _ptr(x), c_longlong(_rows(x, "x")), _ptr(w),
+                                  c_int(dtype_code(x.dtype)), c_int(T), c_int(heads), c_int(D), c_int(N), c_int(extra),
+                                  _stream()))
+
+
+# ---------------------------------------------------------------- the norm without statistics, and re-entry
+
+def tanh_norm(y, x, w, b, alpha: float, rows=None) -> None:
+    """y = tanh(alpha x) w + b (32-bit), of the listed rows of x when ``rows`` is given."""
+    n, H = y.shape
+    if not y.is_contiguous() or not x.is_contiguous() or x.shape[1] != H or w.numel() != H or b.numel() != H:
+        raise KernelError("tanh_norm: shapes do not fit")
+    if rows is None and x.shape[0] != n:
+        raise KernelError("tanh_norm: as many rows out as in")
+    _check(_lib().af_tanh_norm(_ptr(y), c_int(dtype_code(y.dtype)), _ptr(x, "x", torch.float32),
+                               _ptr(w, "w", torch.float32), _ptr(b, "b", torch.float32), c_float(alpha),
+                               _ptr(rows, "rows", torch.int32, allow_none=True), c_int(n), c_int(H), _stream()))
+
+
+def add_tanh_norm(x, a, w, b, alpha: float, y=None, w_next=None, b_next=None, alpha_next: float = 0.0) -> None:
+    """x += tanh(alpha a) w + b in place (32-bit); ``a`` [rows, H] of the compute dtype or float32, or float32
+    partial sums [n, rows, H] added in index order first.  With ``y``: also y = tanh(alpha_next x) w_next + b_next."""
+    n, H = x.shape
+    parts = a.shape[0] if a.dim() == 3 else 1
+    if not x.is_contiguous() or not a.is_contiguous() or tuple(a.shape[-2:]) != (n, H) or (y is not None and not y.is_contiguous()):
+        raise KernelError("add_tanh_norm: shapes do not fit")
+    _check(_lib().af_add_tanh_norm(
+        _ptr(x, "x", torch.float32), _ptr(a), c_int(dtype_code(a.dtype)), c_int(parts), c_longlong(n * H),
+        _ptr(w, "w", torch.float32), _ptr(b, "b", torch.float32), c_float(alpha), _ptr(y, "y", allow_none=True),
+        c_int(dtype_code(y.dtype) if y is not None else F32), _ptr(w_next, "w_next", torch.float32, allow_none=True),
+        _ptr(b_next, "b_next", torch.float32, allow_none=True), c_float(alpha_next), c_int(n), c_int(H), _stream()))
+
+
+def concat_cast(out, a, b) -> None:
+    """out = [a | b] row by row in out's dtype; a and b float32."""
+    n = out.shape[0]
+    if tuple(out.shape) != (n, a.shape[1] + b.shape[1]) or a.shape[0] != n or b.shape[0] != n \
+            or not (out.is_contiguous() and a.is_contiguous() and b.is_contiguous()):
+        raise KernelError("concat_cast: shapes do not fit")
+    _check(_lib().af_concat_cast(_ptr(out), c_int(dtype_code(out.dtype)), _ptr(a, "a", torch.float32),
+                                 _ptr(b, "b", torch.float32), c_int(n), c_int(a.shape[1]), c_int(b.shape[1]), _stream()))
+
+
+def set_sum_row(x, z, row, y=None, w=None, b=None, alpha: float = 0.0) -> None:
+    """x = z + row for every row (z [rows, H], or float32 partial sums [n, rows, H] added in index order; ``row``
+    float32 [H]); with ``y``: also y = tanh(alpha x) w + b."""
+    n, H = x.shape
+    parts = z.shape[0] if z.dim() == 3 else 1
+    if not x.is_contiguous() or not z.is_contiguous() or tuple(z.shape[-2:]) != (n, H) or row.numel() != H:
+        raise KernelError("set_sum_row: shapes do not fit")
+    _check(_lib().af_set_sum_row(
+        _ptr(x, "x", torch.float32), _ptr(z), c_int(dtype_code(z.dtype)), c_int(parts), c_longlong(n * H),
+        _ptr(row, "row", torch.float32), _ptr(y, "y", allow_none=True),
+        c_int(dtype_code(y.dtype) if y is not None else F32), _ptr(w, "w", torch.float32, allow_none=True),
+        _ptr(b, "b", torch.float32, allow_none=True), c_float(alpha), c_int(n), c_int(H), _stream()))
 
 
 def add_scaled_rmsnorm(x, terms, y=None, w_next=None, eps: float = 0.0, offset: float = 0.0) -> None:

@@ -14,6 +14,15 @@ before any rotation) and values taken from the raw key projection (no
 ``v_weight``: v = W_k h, before norm and rotation).  With either, the
 projection goes into 32-bit rows and one kernel norms, rotates, packs
 [q | k | v] and writes the cache.
+
+More options that go the same way: biases of the q, k and v projections; q and k
+divided by their root mean square per head *after* the rotation (no weight); values
+of another size than the keys (``value_dim``); a chunked mask (``mask`` = "chunk": a
+position sees the earlier positions of its own chunk of ``window`` positions, chunks
+counted from position 0) instead of the sliding one; a learned sink per head in the
+softmax's denominator; an output gate, one number per head and token (the sigmoid of
+a projection of the mixer's input), that multiplies the head's output before the
+output projection.
 """
 from __future__ import annotations
 
@@ -35,7 +44,12 @@ class Attention(Mixer):
     ``o_weight`` (tensor names; ``v_weight`` None or absent: the values are the keys as
     projected); optional ``qk_norm``: {``q_weight``, ``k_weight`` (tensor names of head_dim
     values each), ``eps``}; optional ``wide_output`` (default false): the output projection's
-    result stays float32 on its way into the residual sum; optional ``rope_epilogue`` (default false): run the
+    result stays float32 on its way into the residual sum; optional ``value_dim`` (default ``head_dim``);
+    optional ``mask`` ("window", the default, or "chunk") that says what ``window`` means; optional ``q_bias``,
+    ``k_bias``, ``v_bias`` (tensor names; all or none); ``qk_norm`` may instead be {``after_rotation``: true,
+    ``eps``} (no weights: q and k over their root mean square once they are rotated); optional ``gate_weight``
+    (tensor name, [heads, hidden]: the output gate) and ``sink_weight`` (tensor name, [heads]);
+    optional ``rope_epilogue`` (default false): run the
     q, k, v projection with the rotary encoding and the cache write in its epilogue
     (``kernels.gemm_tc_rope``) where sizes and encoding allow.  Off by default
     because it measures slower than the projection followed by the rotary kernel:
@@ -66,35 +80,57 @@ class Attention(Mixer):
                       self.param("o_weight")]
         self.v_from_k = self.names[2] is None
         self.qk_norm = self.params.get("qk_norm")
+        self.norm_after = bool(self.qk_norm and self.qk_norm.get("after_rotation"))
         if self.qk_norm is not None:
-            missing = [k for k in ("q_weight", "k_weight", "eps") if k not in self.qk_norm]
+            wanted = ("eps",) if self.norm_after else ("q_weight", "k_weight", "eps")
+            missing = [k for k in wanted if k not in self.qk_norm]
             if missing:
                 raise ConfigError(f"attention: 'qk_norm' needs {missing}")
-        # norm or shared values: the projection is packed by the kernel that norms, rotates and stores,
-        # which knows rotations (a rotary encoding or none) and nothing else that rewrites q and k
-        self.packs = self.v_from_k or self.qk_norm is not None
+        self.dv = int(self.params.get("value_dim") or self.hd)
+        self.mask = self.params.get("mask") or "window"
+        if self.mask not in kernels.MASKS:
+            raise ConfigError(f"attention: unknown mask '{self.mask}' (known: {sorted(kernels.MASKS)})")
+        self.bias_names = [self.params.get(k) for k in ("q_bias", "k_bias", "v_bias")]
+        if any(self.bias_names) and not (all(self.bias_names[:2]) and (self.v_from_k or self.bias_names[2])):
+            raise ConfigError("attention: biases for all of q, k and v, or for none")
+        self.gate_name = self.params.get("gate_weight")
+        self.sink_name = self.params.get("sink_weight")
+        if self.v_from_k and self.dv != self.hd:
+            raise ConfigError("attention: values that are the keys have their size")
+        # norm, biases, a gate, shared or odd-sized values: the projection is packed by the kernel that norms,
+        # rotates and stores, which knows rotations (a rotary encoding or none) and nothing else that rewrites q and k
+        self.packs = (self.v_from_k or self.qk_norm is not None or any(self.bias_names) or self.gate_name is not None
+                      or self.dv != self.hd)
         if self.packs and not isinstance(self.position, Rope) \
                 and type(self.position).encode is not PositionEncoding.encode:
             raise ConfigError(f"attention: qk_norm and shared values go with a rotary encoding or none, "
                               f"not with '{self.position.kind}'")
-        self.q_norm_w = self.k_norm_w = None
+        self.q_norm_w = self.k_norm_w = self.bias = self.sinks = None
         self.w_qkv = None
         self.w_o = None
         self.rope_epilogue = False
 
     def kv_need(self):
-        return KVNeed(self.nkv, self.hd, self.window)
+        # (a chunk's keys all lie within the last ``window`` positions: the ring of a window serves it)
+        return KVNeed(self.nkv, self.hd, self.window, None if self.dv == self.hd else self.dv)
 
     def weight_decls(self):
         q, k, v, o = self.names
         decls = [WeightDecl(q, (self.nq * self.hd, self.hidden)),
                  WeightDecl(k, (self.nkv * self.hd, self.hidden))]
         if v is not None:
-            decls.append(WeightDecl(v, (self.nkv * self.hd, self.hidden)))
-        decls.append(WeightDecl(o, (self.hidden, self.nq * self.hd)))
-        if self.qk_norm is not None:
+            decls.append(WeightDecl(v, (self.nkv * self.dv, self.hidden)))
+        decls.append(WeightDecl(o, (self.hidden, self.nq * self.dv)))
+        if self.qk_norm is not None and not self.norm_after:
             decls += [WeightDecl(self.qk_norm["q_weight"], (self.hd,), "norm"),
                       WeightDecl(self.qk_norm["k_weight"], (self.hd,), "norm")]
+        for name, rows in zip(self.bias_names, (self.nq * self.hd, self.nkv * self.hd, self.nkv * self.dv)):
+            if name:
+                decls.append(WeightDecl(name, (rows,), "norm"))
+        if self.gate_name:
+            decls.append(WeightDecl(self.gate_name, (self.nq, self.hidden)))
+        if self.sink_name:
+            decls.append(WeightDecl(self.sink_name, (self.nq,), "norm"))
         return [*decls, *self.position.weight_decls()]
 
     def load(self, weights):
@@ -102,10 +138,16 @@ class Attention(Mixer):
         dt = self.ctx.compute_dtype
         # one matrix product for q, k and v: rows [q heads | k heads | v heads]
         mats = [weights[q], weights[k]] + ([weights[v]] if v is not None else [])
+        if self.gate_name:
+            mats.append(weights[self.gate_name])        # the gate's logits ride behind [q | k | v] in the same product
         self.w_qkv = torch.cat(mats, dim=0).to(dt).contiguous()
+        if any(self.bias_names):
+            self.bias = torch.cat([weights[n].to(torch.float32).reshape(-1) for n in self.bias_names if n]).contiguous()
+        if self.sink_name:
+            self.sinks = weights[self.sink_name].to(torch.float32).contiguous()
         self.w_o = weights[o].to(dt).contiguous()
         self.position.load(weights)
-        if self.qk_norm is not None:
+        if self.qk_norm is not None and not self.norm_after:
             self.q_norm_w = weights[self.qk_norm["q_weight"]].to(torch.float32).contiguous()
             self.k_norm_w = weights[self.qk_norm["k_weight"]].to(torch.float32).contiguous()
         # bfloat16 with a head size and a K that the tensor-core product takes: the rows of every head in the
@@ -124,21 +166,31 @@ class Attention(Mixer):
         return 4 if self.ctx.compute_dtype == torch.float32 else 2
 
     def decode_bytes(self, lens) -> int:
-        weights = (self.w_qkv.shape[0] * self.hidden + self.hidden * self.nq * self.hd) * self._el()
-        kv_row = 2 * self.nkv * self.hd * self._el()
-        return weights + sum(kv_row * (min(n, self.window) if self.window else n) for n in lens)
+        weights = (self.w_qkv.shape[0] * self.hidden + self.hidden * self.nq * self.dv) * self._el()
+        kv_row = self.nkv * (self.hd + self.dv) * self._el()
+        return weights + sum(kv_row * self._visible(n - 1) for n in lens)
+
+    def _visible(self, pos: int) -> int:
+        """Keys that the token at ``pos`` sees."""
+        if not self.window:
+            return pos + 1
+        return pos % self.window + 1 if self.mask == "chunk" else min(pos + 1, self.window)
 
     def score_flops(self, lens) -> int:
         """The part of :meth:`prefill_flops` that is scores and their products with v."""
         pairs = 0
         for n in lens:          # visible (query, key) pairs of a causal prompt, with the window where there is one
             w = self.window
-            pairs += n * (n + 1) // 2 if not w or n <= w else w * (w + 1) // 2 + (n - w) * w
-        return 2 * 2 * pairs * self.nq * self.hd
+            if w and self.mask == "chunk":
+                full, rest = divmod(n, w)
+                pairs += full * (w * (w + 1) // 2) + rest * (rest + 1) // 2
+            else:
+                pairs += n * (n + 1) // 2 if not w or n <= w else w * (w + 1) // 2 + (n - w) * w
+        return 2 * pairs * self.nq * (self.hd + self.dv)
 
     def prefill_flops(self, lens) -> int:
         T = sum(lens)
-        proj = 2 * T * (self.w_qkv.shape[0] * self.hidden + self.hidden * self.nq * self.hd)
+        proj = 2 * T * (self.w_qkv.shape[0] * self.hidden + self.hidden * self.nq * self.dv)
         return proj + self.score_flops(lens)
 
     def _project_rotate_store(self, x, batch, view):
@@ -165,7 +217,7 @@ class Attention(Mixer):
         (from the raw key projection, or their own heads), all packed and the cache written: one kernel."""
         nq, nkv, hd = self.nq, self.nkv, self.hd
         proj = linear(x, self.w_qkv, out_dtype=torch.float32)
-        qkv = torch.empty(x.shape[0], (nq + 2 * nkv) * hd, dtype=x.dtype, device=x.device)
+        qkv = torch.empty(x.shape[0], (nq + nkv) * hd + nkv * self.dv, dtype=x.dtype, device=x.device)
         rope = self.position if isinstance(self.position, Rope) else None
         if rope is not None and rope.rotary_dim > hd:
             raise ConfigError(f"rope: rotary_dim {rope.rotary_dim} exceeds head_dim {hd}")
@@ -175,14 +227,20 @@ class Attention(Mixer):
             rope.rotary_dim if rope is not None else 0, rope.pairing if rope is not None else "half",
             q_weight=self.q_norm_w, k_weight=self.k_norm_w,
             eps=float(self.qk_norm["eps"]) if self.qk_norm is not None else 0.0,
-            v_from_k=self.v_from_k, kv=view.kv if view.writes else None)
-        return qkv
+            v_from_k=self.v_from_k, kv=view.kv if view.writes else None, bias=self.bias,
+            norm_after=self.norm_after, magnitude=rope.magnitude if rope is not None else 1.0, dv=self.dv)
+        gate = None
+        if self.gate_name:
+            at = (nq + nkv) * hd + (0 if self.v_from_k else nkv * self.dv)
+            gate = proj[:, at: at + nq]
+        return qkv, gate
 
     def forward(self, x, batch, view):
         nq, nkv, hd = self.nq, self.nkv, self.hd
         kv = view.kv
+        gate = None
         if self.packs:
-            qkv = self._project_norm_pack(x, batch, view)
+            qkv, gate = self._project_norm_pack(x, batch, view)
         elif self.rope_epilogue:
             qkv = self._project_rotate_store(x, batch, view)
         else:
@@ -202,14 +260,15 @@ class Attention(Mixer):
         q = qkv[:, : nq * hd]
         k = qkv[:, nq * hd: (nq + nkv) * hd]
         v = qkv[:, (nq + nkv) * hd:]
-        ctx = torch.empty(x.shape[0], nq * hd, dtype=x.dtype, device=x.device)
+        ctx = torch.empty(x.shape[0], nq * self.dv, dtype=x.dtype, device=x.device)
         window = self.window or 0
+        more = {"dv": self.dv, "mask": self.mask, "sinks": self.sinks, "gate": gate}
         if batch.is_prefill:
             if not view.writes:
                 k, v = batch.step_kv[view.cache_id]
             elif view.keep_step_kv:
                 batch.step_kv[view.cache_id] = (k.clone(), v.clone())
-            kernels.attn_prefill(ctx, q, k, v, batch, nq, nkv, hd, self.scale, self.softcap, window, slopes)
+            kernels.attn_prefill(ctx, q, k, v, batch, nq, nkv, hd, self.scale, self.softcap, window, slopes, **more)
         else:
-            kernels.attn_decode(ctx, q, kv, batch, nq, nkv, hd, self.scale, self.softcap, window, slopes)
+            kernels.attn_decode(ctx, q, kv, batch, nq, nkv, hd, self.scale, self.softcap, window, slopes, **more)
         return linear_split(ctx, self.w_o, wide=bool(self.params.get("wide_output", False)))

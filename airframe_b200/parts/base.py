@@ -2,7 +2,8 @@
 
 Five categories: ``norm``, ``position``, ``mixer``, ``feed_forward`` and
 ``block`` (the arrangement of the other four in a layer), plus ``embedding``
-and ``head`` at the model's ends.  A part is built from the parameters of its
+and ``head`` at the model's ends and ``junction`` (what happens to the
+residual stream between two runs of the schedule).  A part is built from the parameters of its
 :class:`~airframe_b200.config.PartSpec` alone: it takes every size and
 constant from there and does not know which model it is in.  New kinds are
 added with :func:`register_part`; nothing else has to change.
@@ -19,7 +20,7 @@ import torch
 
 from ..config.base import ConfigError, PartSpec
 
-CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block", "embedding", "head")
+CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block", "embedding", "head", "junction")
 _REGISTRY: dict = {c: {} for c in CATEGORIES}
 
 
@@ -66,10 +67,17 @@ def build_part(category: str, spec: PartSpec, ctx: BuildContext, **children):
 @dataclass(frozen=True)
 class KVNeed:
     """Keys and values per token.  ``window`` None: all of them are kept;
-    otherwise the last ``window`` rows (a ring)."""
+    otherwise the last ``window`` rows (a ring).  ``value_dim``: the size of a
+    value row (None: ``head_dim``, as the keys; 0: no value pages, the mixer finds
+    its values inside the key rows)."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    value_dim: Optional[int] = None
+
+    @property
+    def value_size(self) -> int:
+        return self.head_dim if self.value_dim is None else self.value_dim
 
 
 @dataclass(frozen=True)
@@ -218,6 +226,19 @@ class FeedForward(Part):
 
     def forward(self, x, batch):
         """x [T, H] compute dtype -> [T, H] compute dtype."""
+        raise NotImplementedError
+
+
+class Junction(Part):
+    """What happens to the residual stream between two runs of the schedule (a
+    schedule entry names one with ``enter``)."""
+
+    def forward(self, x, x0, index: int, batch, then=None, out_dtype=None):
+        """Rewrite the float32 residual stream x [T, H] in place.  ``x0`` is the
+        embedding's output of the step, ``index`` the schedule entry's
+        ``enter_index`` (the number of the pass, for one that differs from pass to
+        pass).  With ``then`` (the norm that the next run applies first) returns
+        then.forward(x) in ``out_dtype``, else None."""
         raise NotImplementedError
 
 

@@ -1,7 +1,8 @@
 """Arrangements of a layer's parts around the float32 residual stream.
 
 ``sandwich``: x += post(mixer(pre(x))); x += post(ff(pre(x))) - norms before
-and after both halves (reference order
+and after both halves; a layer whose feed-forward is of the kind ``none`` has
+the first half only (reference order
 ``src/backend/bindless/pipeline/inference.rs:1096-1251``, net effect
 x + norm(a) of ``sh_layer_v1.wgsl:834-849,869-884``).
 ``prenorm``: x += mixer(pre(x)); x += ff(pre(x)); a layer whose feed-forward
@@ -20,6 +21,11 @@ from .linear import as_terms
 class SandwichBlock(Block):
     roles = ("pre_mixer", "post_mixer", "pre_feed_forward", "post_feed_forward")
 
+    def __init__(self, params, ctx, mixer, feed_forward, norms):
+        if not feed_forward.present:
+            self.roles = ("pre_mixer", "post_mixer")
+        super().__init__(params, ctx, mixer, feed_forward, norms)
+
     def forward(self, x, batch, view, normed=None, next_pre=None):
         """Updates x in place.  ``normed`` may carry pre_mixer(x) made by the
         previous layer's last kernel; ``next_pre`` is the next layer's first
@@ -28,6 +34,8 @@ class SandwichBlock(Block):
         dt = self.ctx.compute_dtype
         h = normed if normed is not None else n["pre_mixer"].forward(x, dt)
         a = self.mixer.forward(h, batch, view)
+        if not self.feed_forward.present:
+            return n["post_mixer"].add_normed(x, a, then=next_pre, out_dtype=dt)
         h = n["post_mixer"].add_normed(x, a, then=n["pre_feed_forward"], out_dtype=dt)
         f = self.feed_forward.forward(h, batch)
         return n["post_feed_forward"].add_normed(x, f, then=next_pre, out_dtype=dt)

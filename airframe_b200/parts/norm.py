@@ -1,4 +1,8 @@
-"""RMS norm with a weight offset: y = x * rsqrt(mean(x^2) + eps) * (offset + w).
+"""Norms of the residual stream.
+
+``rms_norm``: y = x * rsqrt(mean(x^2) + eps) * (offset + w).
+``tanh_norm``: y = tanh(alpha x) w + b with a scalar alpha: no mean and no
+variance, so it is elementwise and a row needs no reduction.
 
 Reference: ``src/backend/bindless/sh_layer_v1.wgsl:426-451``,
 ``src/backend/bindless/sh_rmsnorm.wgsl:69-93``; post norms fused with the
@@ -65,4 +69,52 @@ class RmsNorm(Norm):
         of the new x, in one kernel."""
         y = torch.empty(x.shape[0], self.size, dtype=out_dtype, device=x.device)
         kernels.add_scaled_rmsnorm(x, as_terms(a), y=y, w_next=self.w, eps=self.eps, offset=self.offset)
+        return y
+
+
+@register_part("norm", "tanh_norm")
+class TanhNorm(Norm):
+    """y = tanh(alpha x) w + b.  Parameters: ``weight``, ``bias``, ``alpha`` (tensor names; alpha a scalar), ``size``."""
+    graph_safe = True
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.names = (self.param("weight"), self.param("bias"), self.param("alpha"))
+        self.size = int(self.param("size"))
+        self.w = self.b = None
+        self.alpha = 0.0
+
+    def weight_decls(self):
+        w, b, a = self.names
+        return [WeightDecl(w, (self.size,), "norm"), WeightDecl(b, (self.size,), "norm"), WeightDecl(a, (), "norm")]
+
+    def load(self, weights):
+        w, b, a = self.names
+        self.w = weights[w].to(torch.float32).contiguous()
+        self.b = weights[b].to(torch.float32).contiguous()
+        self.alpha = float(weights[a].to(torch.float32).item())      # (read once, when the model loads)
+
+    def decode_bytes(self, lens) -> int:
+        return 8 * self.size
+
+    def forward(self, x, out_dtype, rows=None):
+        n = x.shape[0] if rows is None else rows.shape[0]
+        y = torch.empty(n, self.size, dtype=out_dtype, device=x.device)
+        kernels.tanh_norm(y, x, self.w, self.b, self.alpha, rows)
+        return y
+
+    def add_normed(self, x, a, then=None, out_dtype=None):
+        """x += this norm of ``a``; with ``then`` (a norm of this kind) its output for the new x comes out of the
+        same kernel."""
+        if isinstance(a, PartialSums):
+            a = a.parts
+        if then is not None and not isinstance(then, TanhNorm):
+            kernels.add_tanh_norm(x, a, self.w, self.b, self.alpha)
+            return then.forward(x, out_dtype)
+        y = None
+        if then is not None:
+            y = torch.empty(x.shape[0], self.size, dtype=out_dtype, device=x.device)
+        kernels.add_tanh_norm(x, a, self.w, self.b, self.alpha, y=y, w_next=then.w if then is not None else None,
+                              b_next=then.b if then is not None else None,
+                              alpha_next=then.alpha if then is not None else 0.0)
         return y

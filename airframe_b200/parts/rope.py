@@ -8,8 +8,16 @@ of inverse frequencies made in 64 bits.  Reference: ``theta_p`` of
 ``src/backend/bindless/sh_layer_v1.wgsl:706-725`` (relative, at score time).
 The reference pairs adjacent elements (GGUF row order); ``pairing`` selects
 ``half`` (element i with i + rotary_dim/2, Hugging Face row order) or ``adjacent``.
+
+``scaling`` stretches the context a model was trained for: with
+turn(t) = rotary_dim * ln(original / (2 pi t)) / (2 ln theta), lo = max(floor(turn(fast)), 0) and
+hi = min(ceil(turn(slow)), rotary_dim - 1), pair p gets the ramp r = clamp((p - lo) / max(hi - lo, 0.001), 0, 1) and
+the frequency f_p / factor * r + f_p * (1 - r): fast pairs keep their frequency, slow ones are
+divided by ``factor``.  Cosines and sines are then multiplied by ``magnitude`` = 0.1 ln(factor) + 1.
 """
 from __future__ import annotations
+
+import math
 
 import torch
 
@@ -20,7 +28,8 @@ from .base import PositionEncoding, register_part
 
 @register_part("position", "rope")
 class Rope(PositionEncoding):
-    """Parameters: ``theta``, ``rotary_dim``, ``pairing``."""
+    """Parameters: ``theta``, ``rotary_dim``, ``pairing``; optional ``scaling``: {``factor``, ``original``,
+    ``fast``, ``slow``}."""
     graph_safe = True
 
 
@@ -35,6 +44,24 @@ class Rope(PositionEncoding):
             raise ConfigError(f"rope: unknown pairing '{self.pairing}'")
         p = torch.arange(self.rotary_dim // 2, dtype=torch.float64)
         inv = torch.tensor(self.theta, dtype=torch.float64) ** (-2.0 * p / max(self.rotary_dim, 1))
+        self.magnitude = 1.0
+        sc = self.params.get("scaling")
+        if sc:
+            missing = [k for k in ("factor", "original", "fast", "slow") if k not in sc]
+            if missing:
+                raise ConfigError(f"rope: 'scaling' needs {missing}")
+            factor, original = float(sc["factor"]), float(sc["original"])
+            if not (factor > 0 and original > 0 and float(sc["fast"]) > 0 and float(sc["slow"]) > 0 and self.theta > 1):
+                raise ConfigError("rope: 'scaling' needs positive numbers and theta > 1")
+
+            def turn(t):
+                return self.rotary_dim * math.log(original / (2.0 * math.pi * t)) / (2.0 * math.log(self.theta))
+
+            lo = max(math.floor(turn(float(sc["fast"]))), 0)
+            hi = min(math.ceil(turn(float(sc["slow"]))), self.rotary_dim - 1)
+            ramp = ((p - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+            inv = inv / factor * ramp + inv * (1.0 - ramp)
+            self.magnitude = 0.1 * math.log(factor) + 1.0
         self._inv_freq_host = inv.to(torch.float32)
         self.inv_freq = None
 
@@ -42,15 +69,21 @@ class Rope(PositionEncoding):
         self.inv_freq = self._inv_freq_host.to(self.ctx.device)
 
     def rotates_half_pairs(self, hd):
-        return self.pairing == "half" and self.rotary_dim == hd
+        return self.pairing == "half" and self.rotary_dim == hd and self.magnitude == 1.0
+
+    def _plain_only(self):
+        if self.magnitude != 1.0:
+            raise ConfigError("rope: stretched frequencies with a magnitude go through the mixer's packing kernel "
+                              "(kernels.qk_norm_rope_store), which this path is not")
 
     def rotary_table(self, batch, hd):
-        key = ("rope_table", self.theta, self.rotary_dim)
+        key = ("rope_table", self.theta, self.rotary_dim, self.inv_freq.data_ptr())
         if key not in batch.aux:
             batch.aux[key] = kernels.rope_table(batch.positions, self.inv_freq)
         return batch.aux[key]
 
     def encode(self, qkv, batch, nq, nkv, hd, parts=None):
+        self._plain_only()
         if self.rotary_dim > hd:
             raise ConfigError(f"rope: rotary_dim {self.rotary_dim} exceeds head_dim {hd}")
         kernels.rope_cache_write(qkv, batch.positions, self.inv_freq, nq, nkv, hd, self.rotary_dim,
@@ -59,6 +92,7 @@ class Rope(PositionEncoding):
     def encode_and_store(self, qkv, batch, nq, nkv, hd, kv, parts=None) -> bool:
         """The rotation and the mixer's cache store as one kernel (the rotated
         k rows are what the cache keeps)."""
+        self._plain_only()
         if self.rotary_dim > hd:
             raise ConfigError(f"rope: rotary_dim {self.rotary_dim} exceeds head_dim {hd}")
         # many rows (a prompt): the cosines and sines come from the step's table, made once for all layers
