@@ -1,5 +1,5 @@
 """Named configurations for the random-weights mode: the two tiny test
-models, the layer sizes of the released Gemma-2 models and a small Fiferax, as
+models, the layer sizes of the released Gemma-2 models, a small Fiferax and a small Banitar, as
 config.json dictionaries.  Nothing here is read by the model code: a configuration always
 reaches it through ``config_from_dict``."""
 from __future__ import annotations
@@ -49,6 +49,23 @@ def _fiferax_small() -> dict:
 
 
 PRESETS["fiferax-small"] = _fiferax_small()
+
+
+def _banitar_small() -> dict:
+    """Banitar with four layers, the two in the middle run twice (sizes of no released model)."""
+    attn = {"heads": 8, "kv_heads": 2, "dim": 64, "vdim": 64, "mask": {"size": 256}, "scale": 0.125,
+            "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 512, "fast": 32.0, "slow": 1.0}}}
+    latent = {"heads": 8, "dim": 32, "rot_dim": 32, "vdim": 64, "kv_rank": 128, "mask": {"size": 192}, "scale": 0.125,
+              "rot": {"base": 10000.0, "dims": 32}}
+    layers = [{"type": "attention", "mixer": attn, "mlp": {"kind": "dense", "ff": 1536}},
+              {"type": "latent_attention", "mixer": latent, "mlp": {"kind": "dense", "ff": 1536}},
+              {"type": "attention", "mixer": attn, "mlp": None},
+              {"type": "latent_attention", "mixer": latent, "mlp": {"kind": "dense", "ff": 1536}}]
+    return {"architecture": "Banitar", "vocab": 8192, "width": 512, "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-6}, "layers": layers, "loop": {"start": 1, "stop": 3, "times": 2}}
+
+
+PRESETS["banitar-small"] = _banitar_small()
 
 
 def preset(name: str) -> dict:

@@ -218,3 +218,10 @@ def logits(cfg, W, tokens):
     """Logits [T, vocab] at every position of one sequence."""
     x = residual_streams(cfg, W, tokens)[-1]
     return tanh_norm(x, W, "final.norm") @ W["head"].T
+
+
+def generate_greedy(cfg, W, prompt, n):
+    ids = list(prompt)
+    for _ in range(n):
+        ids.append(int(torch.argmax(logits(cfg, W, ids)[-1])))
+    return ids[len(prompt):]
