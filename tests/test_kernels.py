@@ -550,9 +550,9 @@ def test_kernels_refuse_what_they_cannot_do(K):
         K.rmsnorm(x, x, x[0], 1e-6, 1.0)
     with pytest.raises(K.KernelError, match="float32 or bfloat16"):
         K.dtype_code(torch.float16)
-    q = torch.zeros(1, 528, device=DEV)
-    with pytest.raises(K.KernelError, match="head_dim 528"):
-        K.attn_prefill_plain(q, q, q, q, torch.zeros(1, dtype=torch.int32, device=DEV), 1, 1, 528, 1.0, 0.0, 0)
+    q = torch.zeros(1, 656, device=DEV)
+    with pytest.raises(K.KernelError, match="key size 656"):
+        K.attn_prefill_plain(q, q, q, q, torch.zeros(1, dtype=torch.int32, device=DEV), 1, 1, 656, 1.0, 0.0, 0)
     with pytest.raises(K.KernelError, match="heads 3, groups 2"):
         K.attn_prefill_plain(q, q, q, q, torch.zeros(1, dtype=torch.int32, device=DEV), 3, 2, 16, 1.0, 0.0, 0)
 
