@@ -30,6 +30,7 @@ the model's parts (``Model.decode_bytes``, ``Model.prefill_flops``).
 ``--fiferax all|w1024|w2304|w4096`` (not the default run) prints, for layer sizes like a real model's, one line
 for Fiferax and one for Gemma-2 of equal width, depth, feed-forward and vocabulary: prefill of one prompt of
 2,048 tokens, decode at batch 8 after such prompts, and the device time of every kernel of both.
+``--banitar all|w1024|w2304|w4096|w4096-192`` does the same for Banitar.
 """
 from __future__ import annotations
 
@@ -482,6 +483,50 @@ def fiferax_points(args) -> None:
     """Prefill (one prompt of 2,048 tokens) and decode (batch 8 after such prompts, the captured step, logits
     out) of Fiferax at a few layer sizes, each beside the Gemma-2 model of equal width, depth, feed-forward and
     vocabulary; and where a step's time goes, kernel by kernel.  One JSON line a model."""
+    side_by_side(args, args.fiferax, FIFERAX_POINTS, _fiferax_sizes, "fiferax")
+
+
+def _banitar_sizes(width, layers, heads, kv_heads, attn_dim, lat_dim, rot_dim, vdim, kv_rank, window, ff, vocab):
+    """A Banitar model of `layers` layers, attention and latent attention in turn, of which the third and fourth
+    run twice, and the Gemma-2 model of the same width, feed-forward and vocabulary with as many layers as that
+    makes runs."""
+    attn = {"heads": heads, "kv_heads": kv_heads, "dim": attn_dim, "vdim": attn_dim, "mask": {"size": window},
+            "scale": attn_dim ** -0.5, "rot": {"base": 1e6, "dims": attn_dim,
+                                              "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+    latent = {"heads": heads, "dim": lat_dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank,
+              "mask": {"size": window}, "scale": (lat_dim + rot_dim) ** -0.5, "rot": {"base": 1e4, "dims": rot_dim}}
+    bn = {"architecture": "Banitar", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+          "layers": [{"type": "attention" if i % 2 == 0 else "latent_attention", "mixer": attn if i % 2 == 0 else latent,
+                      "mlp": {"kind": "dense", "ff": ff}} for i in range(layers)],
+          "loop": {"start": 2, "stop": 4, "times": 2}}
+    gemma = dict(GEMMA2_2B, num_hidden_layers=layers + 2, hidden_size=width, num_attention_heads=heads,
+                 num_key_value_heads=kv_heads, head_dim=attn_dim, intermediate_size=ff, vocab_size=vocab,
+                 sliding_window=window, query_pre_attn_scalar=attn_dim)
+    return bn, gemma
+
+
+BANITAR_POINTS = {
+    "w1024": dict(width=1024, layers=8, heads=16, kv_heads=4, attn_dim=64, lat_dim=32, rot_dim=32, vdim=64, kv_rank=128,
+                  window=1024, ff=4096, vocab=32000),
+    "w2304": dict(width=2304, layers=8, heads=18, kv_heads=6, attn_dim=128, lat_dim=64, rot_dim=64, vdim=128,
+                  kv_rank=256, window=4096, ff=9216, vocab=32000),
+    "w4096": dict(width=4096, layers=8, heads=32, kv_heads=8, attn_dim=128, lat_dim=64, rot_dim=64, vdim=128,
+                  kv_rank=512, window=4096, ff=14336, vocab=32000),
+    # a latent head whose key (128 + 64) and value (128) sizes differ
+    "w4096-192": dict(width=4096, layers=8, heads=32, kv_heads=8, attn_dim=128, lat_dim=128, rot_dim=64, vdim=128,
+                      kv_rank=512, window=4096, ff=14336, vocab=32000),
+}
+
+
+def banitar_points(args) -> None:
+    """The same figures for Banitar (attention with a chunked mask and latent attention in turn, two of the layers
+    run twice) beside the Gemma-2 model of equal width, feed-forward, heads, vocabulary and number of runs."""
+    side_by_side(args, args.banitar, BANITAR_POINTS, _banitar_sizes, "banitar")
+
+
+def side_by_side(args, which, points, make, arm_name) -> None:
+    """Prefill and decode of a design at the named points, each beside the Gemma-2 model that `make` pairs it
+    with.  One JSON line a model."""
     import torch
     sys.path.insert(0, str(ROOT))
     from torch.profiler import ProfilerActivity, profile
@@ -521,10 +566,10 @@ def fiferax_points(args) -> None:
             out[name] = (n + 1, us + own)
         return {k: {"n": n, "us": round(us, 1)} for k, (n, us) in sorted(out.items(), key=lambda kv: -kv[1][1])}
 
-    for tag, sizes in FIFERAX_POINTS.items():
-        if args.fiferax not in ("all", tag):
+    for tag, sizes in points.items():
+        if which not in ("all", tag):
             continue
-        for arm, cfg_dict in zip(("fiferax", "gemma2"), _fiferax_sizes(**sizes)):
+        for arm, cfg_dict in zip((arm_name, "gemma2"), make(**sizes)):
             cfg = config_from_dict(cfg_dict)
             V = cfg_dict.get("vocab") or cfg_dict["vocab_size"]
             budget = B * ((P + K + W + 8 + 63) // 64 * 64)
@@ -597,6 +642,8 @@ def main() -> int:
     ap.add_argument("--fiferax", default="", choices=["", "all", *sorted(FIFERAX_POINTS)],
                     help="prefill and decode of Fiferax at layer sizes like a real model's, beside Gemma-2 of equal "
                          "size, then exit (not the default run)")
+    ap.add_argument("--banitar", default="", choices=["", "all", *sorted(BANITAR_POINTS)],
+                    help="the same for Banitar (not the default run)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -611,6 +658,9 @@ def main() -> int:
         return 0
     if args.fiferax:
         fiferax_points(args)
+        return 0
+    if args.banitar:
+        banitar_points(args)
         return 0
     line = run_ours(args)
     if line is not None:
