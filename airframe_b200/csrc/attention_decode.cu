@@ -100,6 +100,12 @@ __device__ __forceinline__ uint32_t da_pack(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// The first position that the token at `pos` sees.  window > 0: the last `window` positions, itself included;
+// window < 0: those of its own chunk of -window positions (chunks counted from position 0); 0: all.
+__device__ __forceinline__ int da_lo(int pos, int window) {
+  return window > 0 ? max(0, pos - window + 1) : (window < 0 ? pos - pos % (-window) : 0);
+}
+
 // Pages of the cache that sequence b's new token attends to: [first, last].
 __device__ __forceinline__ int da_pages(const int* slots, const int* lens, int b, int window, int* first_pp, int* last_pp) {
   const int slot = slots[b], len_b = lens[b];   // (both loads at once: neither waits for the other)
@@ -110,7 +116,7 @@ __device__ __forceinline__ int da_pages(const int* slots, const int* lens, int b
     return 0;
   }
   const int pos = len - 1;
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int lo = da_lo(pos, window);
   *first_pp = lo / AF_PAGE;
   *last_pp = pos / AF_PAGE;
   return *last_pp - *first_pp + 1;
@@ -343,7 +349,7 @@ attn_decode_plan_kernel(int* __restrict__ plan, const int* __restrict__ slots, c
     if (fs.n_pages >= 0) {
       pos = lens[fs.b] - 1;
       slot = slots[fs.b];
-      const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+      const int lo = da_lo(pos, window);
       for (int i = 0; i < 4 && i < fs.n_pages; ++i) {
         const int pp = lo / AF_PAGE + fs.p_in + i;
         const int entry = ring_pages > 0 ? pp % ring_pages : pp;
@@ -445,7 +451,7 @@ attn_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     sg.row_head0 = sg.kvh * group + (y % tiles) * 16;             // head of tile row 0
     sg.n_rows = min(16, sg.kvh * group + group - sg.row_head0);    // heads in this tile
     sg.pos = pos;
-    sg.lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+    sg.lo = da_lo(pos, a.window);
     sg.last_pp = pos / AF_PAGE;        // the page of the new token, which the kernel in front wrote
     sg.pp_begin = sg.lo / AF_PAGE + p_in;
     sg.pt = a.page_table + (size_t)slot * a.max_pages;
@@ -948,8 +954,8 @@ AF_EXPORT int af_attn_decode(void* out, long long out_stride, const void* q, lon
   if (batch == 0) return 0;
   AF_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "af_attn_decode: heads %d, groups %d", nq, nkv);
   AF_REQUIRE(af_attn_decode_supported(hd), "af_attn_decode: head_dim %d (takes 64, 128, 256)", hd);
-  AF_REQUIRE(ring_rows % AF_PAGE == 0 && (ring_rows == 0 || (window > 0 && window <= ring_rows)),
-             "af_attn_decode: window %d, ring rows %d", window, ring_rows);
+  AF_REQUIRE(ring_rows % AF_PAGE == 0 && (ring_rows == 0 || (window != 0 && abs(window) <= ring_rows)),
+             "af_attn_decode: window %d (negative: a chunk), ring rows %d", window, ring_rows);
   AF_REQUIRE(n_splits >= 1 && n_splits <= 65535 && scratch != nullptr, "af_attn_decode: splits %d", n_splits);
   AF_REQUIRE(((uintptr_t)kcache & 15) == 0 && ((uintptr_t)vcache & 15) == 0 && ((uintptr_t)plan & 15) == 0,
              "af_attn_decode: cache and plan alignment");

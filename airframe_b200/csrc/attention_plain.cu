@@ -416,6 +416,8 @@ AF_EXPORT int af_attn_prefill_plain(void* out, int out_stride, const void* q, in
 // One new token per sequence: keys and values come from the cache pages.
 // `lens[b]` counts the new token, which the cache holds already.  Key pages hold rows of `hd` elements,
 // value pages rows of `dv`; with no value pages (vcache null) a value is the first `dv` elements of its key row.
+// A warp per (sequence, head, split): with n_splits > 1 the visible keys are cut into that many equal runs and
+// a warp leaves its run's unnormalised output, maximum and sum in part_o / part_ml for the merge kernel.
 template <typename T>
 __global__ void attn_decode_plain_kernel(T* __restrict__ out, int out_stride, const T* __restrict__ q,
                                          int q_stride, const T* __restrict__ kcache,
@@ -424,44 +426,98 @@ __global__ void attn_decode_plain_kernel(T* __restrict__ out, int out_stride, co
                                          const int* __restrict__ lens, int batch, int nq, int nkv, int hd, int dv,
                                          float scale, float cap, int window, int mask_kind, int ring_rows,
                                          const float* __restrict__ slopes, const float* __restrict__ sinks,
-                                         const float* __restrict__ gate, long long gate_stride) {
+                                         const float* __restrict__ gate, long long gate_stride, int n_splits,
+                                         float* __restrict__ part_o, float* __restrict__ part_ml) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
   const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (w >= (long long)batch * nq) return;
-  const int b = (int)(w / nq), h = (int)(w % nq);
+  if (w >= (long long)batch * nq * n_splits) return;
+  const int split = (int)(w % n_splits);
+  const long long unit = w / n_splits;              // (sequence, head)
+  const int b = (int)(unit / nq), h = (int)(unit % nq);
   const int g = h / (nq / nkv);
   const int slot = slots[b];
   T* o = out + (size_t)b * out_stride + (size_t)h * dv;
   if (slot < 0) {  // padding row
-    for (int d = lane; d < dv; d += 32) o[d] = from_f32<T>(0.f);
+    if (split == 0)
+      for (int d = lane; d < dv; d += 32) o[d] = from_f32<T>(0.f);
+    if (n_splits > 1 && lane == 0) part_ml[2 * w] = -INFINITY, part_ml[2 * w + 1] = 0.f;
     return;
   }
   const int len = lens[b];
   const int pos = len - 1;
   WarpAttn st;
-  attn_load_q(st, q + (size_t)b * q_stride + (size_t)h * hd, hd, lane, sinks ? sinks[h] : -INFINITY);
-  const int lo = first_visible(pos, window, mask_kind);
+  // (with splits the sink joins in the merge)
+  attn_load_q(st, q + (size_t)b * q_stride + (size_t)h * hd, hd, lane, sinks && n_splits == 1 ? sinks[h] : -INFINITY);
+  int lo = first_visible(pos, window, mask_kind), hi = pos;
+  if (n_splits > 1) {
+    const int per = (pos - lo + n_splits) / n_splits;       // ceil((pos - lo + 1) / n_splits)
+    lo += split * per;
+    hi = min(pos, lo + per - 1);
+  }
   const int* pt = page_table + (size_t)slot * max_pages;
   const float slope = slopes ? slopes[h] : 0.f;
-  for (int j = lo; j <= pos; ++j) {
+  for (int j = lo; j <= hi; ++j) {
     const int r = ring_rows > 0 ? j % ring_rows : j;
     if (!AF_INDEX_OK(r / AF_PAGE < max_pages && pt[r / AF_PAGE] >= 0, r)) continue;
     const size_t row = ((size_t)pt[r / AF_PAGE] * nkv + g) * AF_PAGE + r % AF_PAGE;
     const T* kr = kcache + row * hd;
     attn_key(st, kr, vcache ? vcache + row * dv : kr, hd, dv, lane, scale, cap, slope * (float)(j - pos));
   }
-  attn_store(st, o, dv, lane, gate_factor(gate, gate_stride, b, h));
+  if (n_splits == 1) {
+    attn_store(st, o, dv, lane, gate_factor(gate, gate_stride, b, h));
+    return;
+  }
+  float* po = part_o + (size_t)w * dv;
+#pragma unroll
+  for (int e = 0; e < AF_HD_SLICES; ++e) {
+    const int d = lane + 32 * e;
+    if (d < dv) po[d] = st.o[e];
+  }
+  if (lane == 0) part_ml[2 * w] = st.m, part_ml[2 * w + 1] = st.l;
 }
 
+// Joins the splits of a (sequence, head): out = sum_s o_s e^(m_s - M) / (sum_s l_s e^(m_s - M) + e^(sink - M)),
+// times the gate's factor.  One block per (sequence, head), threads over the value's elements.
+template <typename T>
+__global__ void __launch_bounds__(128)
+attn_decode_plain_merge_kernel(T* __restrict__ out, int out_stride, const float* __restrict__ part_o,
+                               const float* __restrict__ part_ml, const int* __restrict__ slots, int nq, int dv,
+                               int n_splits, const float* __restrict__ sinks, const float* __restrict__ gate,
+                               long long gate_stride) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int b = blockIdx.x, h = blockIdx.y;
+  if (slots[b] < 0) return;                                  // (a padding row: the split kernel wrote zeros)
+  const size_t u = ((size_t)b * nq + h) * n_splits;
+  float M = sinks ? sinks[h] : -INFINITY;
+  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[2 * (u + s)]);
+  float L = sinks ? expf(sinks[h] - M) : 0.f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float m = part_ml[2 * (u + s)];
+    if (m > -INFINITY) L += part_ml[2 * (u + s) + 1] * expf(m - M);
+  }
+  const float inv = L > 0.f ? gate_factor(gate, gate_stride, b, h) / L : 0.f;
+  T* o = out + (size_t)b * out_stride + (size_t)h * dv;
+  for (int d = threadIdx.x; d < dv; d += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float m = part_ml[2 * (u + s)];
+      if (m > -INFINITY) acc += part_o[(u + s) * dv + d] * expf(m - M);
+    }
+    o[d] = from_f32<T>(acc * inv);
+  }
+}
+
+// `scratch`: n_splits > 1 needs batch * nq * n_splits * (dv + 2) floats.
 AF_EXPORT int af_attn_decode_plain(void* out, int out_stride, const void* q, int q_stride,
                                    const void* kcache, const void* vcache, int dtype,
                                    const int* page_table, int max_pages, const int* slots,
                                    const int* lens, int batch, int nq, int nkv, int hd, int dv, float scale,
                                    float cap, int window, int mask_kind, int ring_rows, const float* slopes,
-                                   const float* sinks, const float* gate, long long gate_stride,
-                                   cudaStream_t stream) {
+                                   const float* sinks, const float* gate, long long gate_stride, int n_splits,
+                                   float* scratch, cudaStream_t stream) {
   if (batch == 0) return 0;
   AF_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "af_attn_decode_plain: heads %d, groups %d", nq, nkv);
   AF_REQUIRE(hd > 0 && hd <= AF_MAX_HD && dv > 0 && dv <= AF_MAX_HD && (vcache != nullptr || dv <= hd),
@@ -470,15 +526,55 @@ AF_EXPORT int af_attn_decode_plain(void* out, int out_stride, const void* q, int
   AF_REQUIRE(mask_kind == AF_MASK_WINDOW || mask_kind == AF_MASK_CHUNK, "af_attn_decode_plain: mask kind %d", mask_kind);
   AF_REQUIRE(ring_rows % AF_PAGE == 0 && (ring_rows == 0 || window > 0) && (window <= ring_rows || ring_rows == 0),
              "af_attn_decode_plain: window %d, ring rows %d", window, ring_rows);
-  const long long warps = (long long)batch * nq;
+  AF_REQUIRE(n_splits >= 1 && (n_splits == 1 || scratch != nullptr) && batch < 65536 && nq < 65536,
+             "af_attn_decode_plain: %d splits need scratch memory", n_splits);
+  const long long warps = (long long)batch * nq * n_splits;
   const int wpb = 4;
   const long long blocks = (warps + wpb - 1) / wpb;
+  AF_REQUIRE(blocks < (1ll << 31), "af_attn_decode_plain: too many rows");
+  float* part_o = scratch;
+  float* part_ml = scratch ? scratch + (size_t)warps * dv : nullptr;
   AF_DISPATCH_DTYPE(dtype, T,
                     af_launch(attn_decode_plain_kernel<T>, dim3((unsigned)blocks), dim3(wpb * 32), 0, stream, 
                         (T*)out, out_stride, (const T*)q, q_stride, (const T*)kcache, (const T*)vcache,
                         page_table, max_pages, slots, lens, batch, nq, nkv, hd, dv, scale, cap, window, mask_kind,
-                        ring_rows, slopes, sinks, gate, gate_stride));
+                        ring_rows, slopes, sinks, gate, gate_stride, n_splits, part_o, part_ml));
+  if (n_splits == 1) AF_CHECK_LAUNCH("af_attn_decode_plain");
+  AF_COUNT_LAUNCH("af_attn_decode_plain");
+  AF_DISPATCH_DTYPE(dtype, T,
+                    af_launch(attn_decode_plain_merge_kernel<T>, dim3(batch, nq), dim3(128), 0, stream, (T*)out,
+                              out_stride, (const float*)part_o, (const float*)part_ml, slots, nq, dv, n_splits, sinks,
+                              gate, gate_stride));
   AF_CHECK_LAUNCH("af_attn_decode_plain");
+}
+
+// An output gate behind an attention kernel that has none of its own: x[t, h, :] *= sigmoid(gate[t, h]).
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_gate_kernel(T* __restrict__ x, long long x_stride, const float* __restrict__ gate, long long gate_stride,
+                 int nq, int dv, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t at = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (at >= total) return;
+  const int per_row = nq * dv;
+  const size_t t = at / per_row;
+  const int i = (int)(at - t * per_row);
+  T* p = x + t * x_stride + i;
+  *p = from_f32<T>(to_f32(*p) * gate_factor(gate, gate_stride, (int)t, i / dv));
+}
+
+AF_EXPORT int af_head_gate(void* x, long long x_stride, int dtype, const float* gate, long long gate_stride, int n_rows,
+                           int nq, int dv, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  AF_REQUIRE(n_rows > 0 && nq > 0 && dv > 0 && gate != nullptr, "af_head_gate: bad sizes");
+  const size_t total = (size_t)n_rows * nq * dv;
+  const size_t blocks = (total + 255) / 256;
+  AF_REQUIRE(blocks < (1ull << 31), "af_head_gate: too many rows");
+  AF_DISPATCH_DTYPE(dtype, T,
+                    af_launch(head_gate_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, (T*)x, x_stride, gate,
+                              gate_stride, nq, dv, total));
+  AF_CHECK_LAUNCH("af_head_gate");
 }
 
 // ---------------------------------------------------------------- norm + rope + cache write from a projection

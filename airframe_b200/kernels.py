@@ -294,11 +294,20 @@ def attn_prefill_plain(out, q, k, v, positions, nq: int, nkv: int, hd: int, scal
         _ptr(sinks, "sinks", torch.float32, allow_none=True), gp, gs, _stream()))
 
 
+def plain_decode_splits(batch: int, nq: int, most_keys: int) -> int:
+    """Into how many runs the plain decode kernel cuts a sequence's visible keys (a warp a run): enough warps
+    for the device's SMs to have some thirty each, no run shorter than 32 keys."""
+    want = -(-sm_count() * 32 // max(1, batch * nq))
+    return max(1, min(want, most_keys // 32, 256))
+
+
 def attn_decode_plain(out, q, kcache, vcache, page_table, slots, lens, nq: int, nkv: int, hd: int,
                       scale: float, cap: float, window: int, ring_rows: int, slopes=None, dv=None,
-                      mask: str = "window", sinks=None, gate=None) -> None:
+                      mask: str = "window", sinks=None, gate=None, n_splits: int = 1) -> None:
     """Attention of one new token per sequence over the cache pages (options as in
-    :func:`attn_prefill_plain`).  ``vcache`` None: a value is the first ``dv`` elements of its key row."""
+    :func:`attn_prefill_plain`).  ``vcache`` None: a value is the first ``dv`` elements of its key row.
+    ``n_splits`` > 1: a sequence's visible keys are cut into that many runs, a warp each, joined by a
+    second kernel."""
     B = q.shape[0]
     if slopes is not None and slopes.numel() != nq:
         raise KernelError(f"attn_decode_plain: {slopes.numel()} slopes for {nq} heads")
@@ -312,6 +321,7 @@ def attn_decode_plain(out, q, kcache, vcache, page_table, slots, lens, nq: int, 
     if tuple(kcache.shape[1:]) != (nkv, PAGE, hd) or (vcache is not None and tuple(vcache.shape[1:]) != (nkv, PAGE, dv)):
         raise KernelError(f"attn_decode_plain: cache pages must be [pages, {nkv}, {PAGE}, {hd}] (values {dv})")
     gp, gs = _gate_args(gate, B, nq, "attn_decode_plain")
+    scratch = torch.empty(B * nq * n_splits * (dv + 2), dtype=torch.float32, device=q.device) if n_splits > 1 else None
     _check(_lib().af_attn_decode_plain(
         _ptr(out), c_int(_rows(out, "out")), _ptr(q), c_int(_rows(q, "q")), _ptr(kcache),
         _ptr(vcache, allow_none=True),
@@ -319,7 +329,7 @@ def attn_decode_plain(out, q, kcache, vcache, page_table, slots, lens, nq: int, 
         _ptr(slots, "slots", torch.int32), _ptr(lens, "lens", torch.int32), c_int(B), c_int(nq), c_int(nkv),
         c_int(hd), c_int(dv), c_float(scale), c_float(cap), c_int(window), c_int(MASKS[mask]), c_int(ring_rows),
         _ptr(slopes, "slopes", torch.float32, allow_none=True), _ptr(sinks, "sinks", torch.float32, allow_none=True),
-        gp, gs, _stream()))
+        gp, gs, c_int(n_splits), _ptr(scratch, "scratch", torch.float32, allow_none=True), _stream()))
 
 
 def add_(x, a) -> None:
@@ -618,26 +628,58 @@ def attn_prefill_tc(out, q, k, v, seq_starts, n_seqs: int, max_len: int, nq, nkv
         c_float(cap), c_int(window), _ptr(error_word(q.device), "err", torch.int32), _stream()))
 
 
+def head_gate(x, gate, nq: int, dv: int) -> None:
+    """x[t, h, :] *= sigmoid(gate[t, h]) for rows x [T, nq dv] (an output gate behind an attention kernel that
+    has none of its own)."""
+    T = x.shape[0]
+    gp, gs = _gate_args(gate, T, nq, "head_gate")
+    _check(_lib().af_head_gate(_ptr(x), c_longlong(_rows(x, "x")), c_int(dtype_code(x.dtype)), gp, gs, c_int(T),
+                               c_int(nq), c_int(dv), _stream()))
+
+
+def _chunk_starts(batch, size: int):
+    """The rows at which the chunks of ``size`` positions of a prefill step's sequences begin (int32 on the
+    device, one more than there are chunks), how many chunks there are and the longest: under a chunked mask every
+    chunk is a causal sequence of its own.  Made once a step (kept in ``batch.aux``)."""
+    key = ("chunk_starts", size)
+    if key not in batch.aux:
+        starts, row = [], 0
+        for n in batch.seq_lens:
+            starts.extend(range(row, row + n, size))
+            row += n
+        starts.append(row)
+        host = torch.tensor(starts, dtype=torch.int32).pin_memory()
+        batch.aux[key] = (host.to(batch.tokens.device, non_blocking=True), len(starts) - 1,
+                          min(size, max(batch.seq_lens)), host)      # (the pinned rows live as long as the copy may wait)
+    return batch.aux[key][:3]
+
+
 def attn_prefill(out, q, k, v, batch, nq, nkv, hd, scale, cap, window, slopes=None, dv=None, mask: str = "window",
                  sinks=None, gate=None) -> None:
     """Attention of a prefill step: for bfloat16 the tcgen05 kernel (head sizes
     128, 256) or the mma.sync kernel (64), else the plain kernel (which also
-    serves scores with a per-head slope, values of another size than the keys, sinks and gates)."""
-    special = (slopes is not None or (dv or hd) != hd or sinks is not None or gate is not None
-               or (mask != "window" and window))
-    if special:
+    serves scores with a per-head slope, values of another size than the keys and sinks).  A chunked mask
+    reaches the fast kernels as what it is: causal attention within chunks that know nothing of one another.
+    A gate behind a fast kernel is a kernel of its own."""
+    fast = q.dtype == torch.bfloat16 and slopes is None and (dv or hd) == hd and sinks is None
+    aligned = all(t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0 for t in (q, k, v, out))
+    use_tc = fast and aligned and bool(_lib().af_attn_prefill_tc_supported(c_int(hd)))
+    use_mma = fast and not use_tc and bool(_lib().af_attn_prefill_supported(c_int(hd))) \
+        and all(t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0 for t in (q, k, v))
+    if not (use_tc or use_mma):
         attn_prefill_plain(out, q, k, v, batch.positions, nq, nkv, hd, scale, cap, window, slopes, dv=dv, mask=mask,
                            sinks=sinks, gate=gate)
         return
-    aligned = all(t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0 for t in (q, k, v, out))
-    if q.dtype == torch.bfloat16 and aligned and _lib().af_attn_prefill_tc_supported(c_int(hd)):
-        attn_prefill_tc(out, q, k, v, batch.seq_starts, batch.n_seqs, batch.max_len, nq, nkv, hd, scale, cap, window)
-        return
-    if (q.dtype == torch.bfloat16 and _lib().af_attn_prefill_supported(c_int(hd))
-            and all(t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0 for t in (q, k, v))):
-        attn_prefill_mma(out, q, k, v, batch.seq_starts, batch.n_seqs, batch.max_len, nq, nkv, hd, scale, cap, window)
-        return
-    attn_prefill_plain(out, q, k, v, batch.positions, nq, nkv, hd, scale, cap, window)
+    starts, n_seqs, max_len = batch.seq_starts, batch.n_seqs, batch.max_len
+    if mask == "chunk" and window:
+        starts, n_seqs, max_len = _chunk_starts(batch, window)
+        window = 0
+    if use_tc:
+        attn_prefill_tc(out, q, k, v, starts, n_seqs, max_len, nq, nkv, hd, scale, cap, window)
+    else:
+        attn_prefill_mma(out, q, k, v, starts, n_seqs, max_len, nq, nkv, hd, scale, cap, window)
+    if gate is not None:
+        head_gate(out, gate, nq, hd)
 
 
 def attn_decode_max_splits(batch: int, nkv: int, max_len: int, window: int, blocks: int = 0, nq: int = 0) -> int:
@@ -647,6 +689,7 @@ def attn_decode_max_splits(batch: int, nkv: int, max_len: int, window: int, bloc
     ``blocks // units of a sequence + 2`` blocks (one long sequence among empty
     ones, whatever the batch) and in at most its pages + 1."""
     blocks = blocks or sm_count()
+    window = abs(window)            # (negative: a chunk of that many positions)
     rows = min(max_len, window) if window else max_len
     pages = max(1, (rows + PAGE - 1) // PAGE + (1 if window else 0))
     tiles = ((nq // nkv) + 15) // 16 if nq else 1
@@ -705,12 +748,14 @@ ATTN_DECODE_MAX_SEQS = 2048     # sequences of a step that the split kernel plan
 def attn_decode(out, q, kv, batch, nq, nkv, hd, scale, cap, window, slopes=None, dv=None, mask: str = "window",
                 sinks=None, gate=None) -> None:
     """Attention of a decode step over the cache: the split kernel for
-    bfloat16 and head sizes it takes, else the plain kernel (which also serves
-    scores with a per-head slope, values of another size than the keys or inside them, sinks and gates)."""
-    special = (slopes is not None or (dv or hd) != hd or kv.v is None or sinks is not None or gate is not None
-               or (mask != "window" and window))
+    bfloat16 and head sizes it takes (a chunked mask goes to it as a negative window, a gate follows it as a
+    kernel of its own), else the plain kernel (which also serves scores with a per-head slope, values of another
+    size than the keys or inside them, and sinks)."""
+    special = slopes is not None or (dv or hd) != hd or kv.v is None or sinks is not None
     if (not special and q.dtype == torch.bfloat16 and _lib().af_attn_decode_supported(c_int(hd))
             and batch.n_seqs <= ATTN_DECODE_MAX_SEQS):
+        if mask == "chunk":
+            window = -window
         n = attn_decode_max_splits(batch.n_seqs, nkv, batch.max_len_after, window, nq=nq)
         # the plan of the step, shared by the layers that read this group of caches alike (a batch without a
         # place for the step's tables gets none: every block then works the cut out itself)
@@ -723,9 +768,14 @@ def attn_decode(out, q, kv, batch, nq, nkv, hd, scale, cap, window, slopes=None,
             plan = aux[key]
         attn_decode_split(out, q, kv.k, kv.v, kv.page_table, batch.slots, batch.len_after, nq, nkv, hd, scale, cap,
                           window, kv.ring_rows, n, plan=plan)
+        if gate is not None:
+            head_gate(out, gate, nq, hd)
         return
+    # (a captured step sizes its cut for the longest context; the keys a token sees are bounded by its window or chunk)
+    most = min(batch.max_len_after, window) if window else batch.max_len_after
     attn_decode_plain(out, q, kv.k, kv.v, kv.page_table, batch.slots, batch.len_after, nq, nkv, hd,
-                      scale, cap, window, kv.ring_rows, slopes, dv=dv, mask=mask, sinks=sinks, gate=gate)
+                      scale, cap, window, kv.ring_rows, slopes, dv=dv, mask=mask, sinks=sinks, gate=gate,
+                      n_splits=plain_decode_splits(batch.n_seqs, nq, most))
 
 
 # ---------------------------------------------------------------- mixers with a state of fixed size
