@@ -719,7 +719,8 @@ AF_EXPORT int af_qk_norm_rope_store(void* qkv, int dtype, long long out_stride, 
 
 // From float projection rows [q heads of (dim + rot) | latent of `rank` | shared key part of `rot`]:
 //   q heads: the last `rot` elements of every head rotated (pairs i, i + rot / 2), the first `dim` kept,
-//            into the rows `q` [heads * (dim + rot)] of the compute dtype;
+//            into the rows `q` of the compute dtype, head u at u * pitch (pitch >= dim + rot; the elements
+//            between a head's end and the next head's start are set to zero);
 //   the latent divided by its root mean square (eps inside the root) times `norm_w`, and the shared key
 //   part rotated, into the row `kv` [rank + rot] of the compute dtype and into the token's row of its cache
 //   page (one kv head of rank + rot elements; the values are the latent part of the same row).
@@ -730,7 +731,7 @@ latent_prep_kernel(T* __restrict__ q, long long q_stride, T* __restrict__ kv, lo
                    const float* __restrict__ proj, long long ld, const float* __restrict__ norm_w, float eps,
                    const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                    const int* __restrict__ slots, const int* __restrict__ len_after,
-                   const float* __restrict__ inv_freq, int heads, int dim, int rot, int rank,
+                   const float* __restrict__ inv_freq, int heads, int dim, int rot, int rank, int pitch,
                    T* __restrict__ kcache, const int* __restrict__ page_table, int max_pages, int ring_rows) {
   pdl_launch_dependents();
   __shared__ float scratch[33];
@@ -773,7 +774,7 @@ latent_prep_kernel(T* __restrict__ q, long long q_stride, T* __restrict__ kv, lo
     const float a = src[p], b = src[p + half];
     const T ra = from_f32<T>(a * c - b * s), rb = from_f32<T>(b * c + a * s);
     if (u < heads) {
-      T* d = qr + (size_t)u * (dim + rot) + dim;
+      T* d = qr + (size_t)u * pitch + dim;
       d[p] = ra, d[p + half] = rb;
     } else {
       kvr[rank + p] = ra, kvr[rank + p + half] = rb;
@@ -782,23 +783,28 @@ latent_prep_kernel(T* __restrict__ q, long long q_stride, T* __restrict__ kv, lo
   }
   for (int i = threadIdx.x; i < heads * dim; i += blockDim.x) {
     const int u = i / dim, e = i - u * dim;
-    qr[(size_t)u * (dim + rot) + e] = from_f32<T>(x[(size_t)u * (dim + rot) + e]);
+    qr[(size_t)u * pitch + e] = from_f32<T>(x[(size_t)u * (dim + rot) + e]);
+  }
+  const int pad = pitch - dim - rot;
+  for (int i = threadIdx.x; i < heads * pad; i += blockDim.x) {
+    const int u = i / pad, e = i - u * pad;
+    qr[(size_t)u * pitch + dim + rot + e] = from_f32<T>(0.f);
   }
 }
 
 AF_EXPORT int af_latent_prep(void* q, long long q_stride, void* kv, long long kv_stride, int dtype, const float* proj,
                              long long ld, const float* norm_w, float eps, const int* positions,
                              const int* seq_of_token, const int* slots, const int* len_after, const float* inv_freq,
-                             int n_tokens, int heads, int dim, int rot, int rank, void* kcache, const int* page_table,
-                             int max_pages, int ring_rows, cudaStream_t stream) {
+                             int n_tokens, int heads, int dim, int rot, int rank, int pitch, void* kcache,
+                             const int* page_table, int max_pages, int ring_rows, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
-  AF_REQUIRE(n_tokens > 0 && heads > 0 && dim >= 0 && rot >= 0 && rot % 2 == 0 && rank > 0 && dim + rot > 0,
-             "af_latent_prep: bad sizes");
+  AF_REQUIRE(n_tokens > 0 && heads > 0 && dim >= 0 && rot >= 0 && rot % 2 == 0 && rank > 0 && dim + rot > 0 &&
+             pitch >= dim + rot, "af_latent_prep: bad sizes");
   AF_REQUIRE(ring_rows % AF_PAGE == 0, "af_latent_prep: ring rows %d not whole pages", ring_rows);
   AF_DISPATCH_DTYPE(dtype, T,
                     af_launch(latent_prep_kernel<T>, dim3(n_tokens), dim3(128), 0, stream, (T*)q, q_stride, (T*)kv,
                               kv_stride, proj, ld, norm_w, eps, positions, seq_of_token, slots, len_after, inv_freq,
-                              heads, dim, rot, rank, (T*)kcache, page_table, max_pages, ring_rows));
+                              heads, dim, rot, rank, pitch, (T*)kcache, page_table, max_pages, ring_rows));
   AF_CHECK_LAUNCH("af_latent_prep");
 }
 

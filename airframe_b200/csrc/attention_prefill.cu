@@ -71,6 +71,9 @@ struct PrefillArgs {
   int nq, nkv;
   float scale, cap;
   int window;
+  const float* sinks;      // [nq] or null: exp(sink) joins a head's softmax denominator (no key, no value)
+  const float* gate;       // float logits or null: row t, head h at gate[t * gate_stride + h]; the head's output times their sigmoid
+  long long gate_stride;
 };
 
 // Byte offset of the 16-byte piece `c` of row `r` in a tile whose rows hold HD bfloat16.
@@ -263,7 +266,10 @@ attn_prefill_mma_kernel(PrefillArgs a) {
   for (int r = 0; r < 2; ++r) {
     const int i = qrow[r];
     if (i >= len) continue;
-    const float inv = sum[r] > 0.f ? 1.f / sum[r] : 0.f;
+    // (scores are base-2 exponents relative to mx: the sink, a natural one, is brought there)
+    if (a.sinks != nullptr) sum[r] += exp2f(a.sinks[head] * LOG2E - mx[r]);
+    float inv = sum[r] > 0.f ? 1.f / sum[r] : 0.f;
+    if (a.gate != nullptr) inv /= 1.f + expf(-a.gate[(size_t)(row0 + i) * a.gate_stride + head]);
     __nv_bfloat16* dst = a.out + (size_t)(row0 + i) * a.out_stride + (size_t)head * HD;
 #pragma unroll
     for (int n = 0; n < ONT; ++n)
@@ -300,7 +306,7 @@ AF_EXPORT int af_attn_prefill_supported(int hd) { return hd == 64 || hd == 128 |
 AF_EXPORT int af_attn_prefill(void* out, long long out_stride, const void* q, long long q_stride, const void* k,
                               long long k_stride, const void* v, long long v_stride, const int* seq_starts,
                               int n_seqs, int max_len, int nq, int nkv, int hd, float scale, float cap, int window,
-                              cudaStream_t stream) {
+                              const float* sinks, const float* gate, long long gate_stride, cudaStream_t stream) {
   if (n_seqs == 0 || max_len == 0) return 0;
   AF_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "af_attn_prefill: heads %d, groups %d", nq, nkv);
   AF_REQUIRE(af_attn_prefill_supported(hd), "af_attn_prefill: head_dim %d (takes 64, 128, 256)", hd);
@@ -310,7 +316,7 @@ AF_EXPORT int af_attn_prefill(void* out, long long out_stride, const void* q, lo
              "af_attn_prefill: operands must be 16-byte aligned");
   AF_REQUIRE(n_seqs <= 65535 && nq <= 65535, "af_attn_prefill: too many sequences or heads");
   PrefillArgs a{(__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k,
-                k_stride, (const __nv_bfloat16*)v, v_stride, seq_starts, nq, nkv, scale, cap, window};
+                k_stride, (const __nv_bfloat16*)v, v_stride, seq_starts, nq, nkv, scale, cap, window, sinks, gate, gate_stride};
   if (hd == 64) return launch_prefill<64>(a, n_seqs, max_len, stream);
   if (hd == 128) return launch_prefill<128>(a, n_seqs, max_len, stream);
   return launch_prefill<256>(a, n_seqs, max_len, stream);

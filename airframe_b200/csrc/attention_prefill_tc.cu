@@ -63,6 +63,9 @@ struct TaArgs {
   float scale, cap;
   int window;
   int* err;
+  const float* sinks;      // [nq] or null: exp(sink) joins a head's softmax denominator (no key, no value)
+  const float* gate;       // float logits or null: row t, head h at gate[t * gate_stride + h]; the head's output times their sigmoid
+  long long gate_stride;
 };
 
 template <int HD>
@@ -391,7 +394,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       float lt = 0.f;
 #pragma unroll
       for (int h = 0; h < 2 * TA_PARTS; ++h) lt += l_s[h * TA_BM + row];
-      const float inv = lt > 0.f ? 1.f / lt : 0.f;
+      // (scores are base-2 exponents: the sink, a natural one, is brought there)
+      if (a.sinks != nullptr) lt += exp2f(a.sinks[head] * TA_LOG2E - __bfloat162float(mref_s[1][row]));
+      float inv = lt > 0.f ? 1.f / lt : 0.f;
+      if (a.gate != nullptr && i < len) inv /= 1.f + expf(-a.gate[(size_t)(row0 + i) * a.gate_stride + head]);
       __nv_bfloat16* dst = a.out + (size_t)(row0 + i) * a.out_stride + (size_t)head * HD + quad * OW;
 #pragma unroll 1
       for (int c0 = 0; c0 < OW; c0 += 32) {
@@ -451,7 +457,8 @@ AF_EXPORT int af_attn_prefill_tc_supported(int hd) { return hd == 128 || hd == 2
 AF_EXPORT int af_attn_prefill_tc(void* out, long long out_stride, const void* q, long long q_stride, const void* k,
                                  long long k_stride, const void* v, long long v_stride, const int* seq_starts,
                                  int n_seqs, int n_tokens, int max_len, int nq, int nkv, int hd, float scale,
-                                 float cap, int window, int* err, cudaStream_t stream) {
+                                 float cap, int window, const float* sinks, const float* gate, long long gate_stride,
+                                 int* err, cudaStream_t stream) {
   if (n_seqs == 0 || max_len == 0) return 0;
   AF_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "af_attn_prefill_tc: heads %d, groups %d", nq, nkv);
   AF_REQUIRE(af_attn_prefill_tc_supported(hd), "af_attn_prefill_tc: head_dim %d (takes 128, 256)", hd);
@@ -467,7 +474,7 @@ AF_EXPORT int af_attn_prefill_tc(void* out, long long out_stride, const void* q,
   if (rc) return rc;
   rc = af_make_map_bf16(&mv, v, n_tokens, (long long)nkv * hd, v_stride, TA_KT);
   if (rc) return rc;
-  TaArgs a{(__nv_bfloat16*)out, out_stride, seq_starts, nq, nkv, scale, cap, window, err};
+  TaArgs a{(__nv_bfloat16*)out, out_stride, seq_starts, nq, nkv, scale, cap, window, err, sinks, gate, gate_stride};
   if (hd == 128) return launch_ta<128>(mq, mk, mv, a, n_seqs, max_len, stream);
   return launch_ta<256>(mq, mk, mv, a, n_seqs, max_len, stream);
 }

@@ -602,21 +602,25 @@ def interleave_gate_up(w_gate, w_up):
     v[:, 1] = u.view(groups, 16, K)
     return out
 
-def attn_prefill_mma(out, q, k, v, seq_starts, n_seqs: int, max_len: int, nq, nkv, hd, scale, cap, window) -> None:
+def attn_prefill_mma(out, q, k, v, seq_starts, n_seqs: int, max_len: int, nq, nkv, hd, scale, cap, window,
+                     sinks=None, gate=None) -> None:
     """bfloat16 prefill attention on the tensor cores; sequences packed row
-    after row, ``seq_starts`` int32 [n_seqs + 1]."""
+    after row, ``seq_starts`` int32 [n_seqs + 1].  ``sinks`` and ``gate`` as in :func:`attn_prefill_plain`."""
+    gp, gs = _gate_args(gate, q.shape[0], nq, "attn_prefill_mma")
     if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("attn_prefill_mma: bfloat16 only")
     _check(_lib().af_attn_prefill(
         _ptr(out), c_longlong(_rows(out, "out")), _ptr(q), c_longlong(_rows(q, "q")), _ptr(k),
         c_longlong(_rows(k, "k")), _ptr(v), c_longlong(_rows(v, "v")), _ptr(seq_starts, "seq_starts", torch.int32),
         c_int(n_seqs), c_int(max_len), c_int(nq), c_int(nkv), c_int(hd), c_float(scale), c_float(cap), c_int(window),
-        _stream()))
+        _ptr(sinks, "sinks", torch.float32, allow_none=True), gp, gs, _stream()))
 
 
-def attn_prefill_tc(out, q, k, v, seq_starts, n_seqs: int, max_len: int, nq, nkv, hd, scale, cap, window) -> None:
+def attn_prefill_tc(out, q, k, v, seq_starts, n_seqs: int, max_len: int, nq, nkv, hd, scale, cap, window,
+                    sinks=None, gate=None) -> None:
     """bfloat16 prefill attention on tcgen05 (S and O in TMEM); sequences packed
-    row after row, ``seq_starts`` int32 [n_seqs + 1]."""
+    row after row, ``seq_starts`` int32 [n_seqs + 1].  ``sinks`` and ``gate`` as in :func:`attn_prefill_plain`."""
+    gp, gs = _gate_args(gate, q.shape[0], nq, "attn_prefill_tc")
     if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("attn_prefill_tc: bfloat16 only")
     if k.shape[0] != q.shape[0] or v.shape[0] != q.shape[0]:
@@ -625,7 +629,8 @@ def attn_prefill_tc(out, q, k, v, seq_starts, n_seqs: int, max_len: int, nq, nkv
         _ptr(out), c_longlong(_rows(out, "out")), _ptr(q), c_longlong(_rows(q, "q")), _ptr(k),
         c_longlong(_rows(k, "k")), _ptr(v), c_longlong(_rows(v, "v")), _ptr(seq_starts, "seq_starts", torch.int32),
         c_int(n_seqs), c_int(q.shape[0]), c_int(max_len), c_int(nq), c_int(nkv), c_int(hd), c_float(scale),
-        c_float(cap), c_int(window), _ptr(error_word(q.device), "err", torch.int32), _stream()))
+        c_float(cap), c_int(window), _ptr(sinks, "sinks", torch.float32, allow_none=True), gp, gs,
+        _ptr(error_word(q.device), "err", torch.int32), _stream()))
 
 
 def head_gate(x, gate, nq: int, dv: int) -> None:
@@ -658,10 +663,9 @@ def attn_prefill(out, q, k, v, batch, nq, nkv, hd, scale, cap, window, slopes=No
                  sinks=None, gate=None) -> None:
     """Attention of a prefill step: for bfloat16 the tcgen05 kernel (head sizes
     128, 256) or the mma.sync kernel (64), else the plain kernel (which also
-    serves scores with a per-head slope, values of another size than the keys and sinks).  A chunked mask
-    reaches the fast kernels as what it is: causal attention within chunks that know nothing of one another.
-    A gate behind a fast kernel is a kernel of its own."""
-    fast = q.dtype == torch.bfloat16 and slopes is None and (dv or hd) == hd and sinks is None
+    serves scores with a per-head slope and values of another size than the keys).  A chunked mask
+    reaches the fast kernels as what it is: causal attention within chunks that know nothing of one another."""
+    fast = q.dtype == torch.bfloat16 and slopes is None and (dv or hd) == hd
     aligned = all(t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0 for t in (q, k, v, out))
     use_tc = fast and aligned and bool(_lib().af_attn_prefill_tc_supported(c_int(hd)))
     use_mma = fast and not use_tc and bool(_lib().af_attn_prefill_supported(c_int(hd))) \
@@ -670,16 +674,17 @@ def attn_prefill(out, q, k, v, batch, nq, nkv, hd, scale, cap, window, slopes=No
         attn_prefill_plain(out, q, k, v, batch.positions, nq, nkv, hd, scale, cap, window, slopes, dv=dv, mask=mask,
                            sinks=sinks, gate=gate)
         return
-    starts, n_seqs, max_len = batch.seq_starts, batch.n_seqs, batch.max_len
+    starts, n_seqs, max_len, size = batch.seq_starts, batch.n_seqs, batch.max_len, window
     if mask == "chunk" and window:
         starts, n_seqs, max_len = _chunk_starts(batch, window)
         window = 0
-    if use_tc:
-        attn_prefill_tc(out, q, k, v, starts, n_seqs, max_len, nq, nkv, hd, scale, cap, window)
+    if n_seqs > 65535:          # (more sequences than a grid's second axis takes)
+        attn_prefill_plain(out, q, k, v, batch.positions, nq, nkv, hd, scale, cap, size, slopes, dv=dv, mask=mask,
+                           sinks=sinks, gate=gate)
+    elif use_tc:
+        attn_prefill_tc(out, q, k, v, starts, n_seqs, max_len, nq, nkv, hd, scale, cap, window, sinks, gate)
     else:
-        attn_prefill_mma(out, q, k, v, starts, n_seqs, max_len, nq, nkv, hd, scale, cap, window)
-    if gate is not None:
-        head_gate(out, gate, nq, hd)
+        attn_prefill_mma(out, q, k, v, starts, n_seqs, max_len, nq, nkv, hd, scale, cap, window, sinks, gate)
 
 
 def attn_decode_max_splits(batch: int, nkv: int, max_len: int, window: int, blocks: int = 0, nq: int = 0) -> int:
@@ -927,15 +932,26 @@ def qk_norm_rope_store(qkv, proj, batch, nq: int, nkv: int, hd: int, inv_freq, r
         _ptr(pt, "page_table", torch.int32, allow_none=True), c_int(max_pages), c_int(ring), _stream()))
 
 
+def attn_prefill_fast_head(size: int) -> int:
+    """The smallest head size that a bfloat16 tensor-core prefill kernel takes and that holds ``size`` elements
+    (a mixer may pad its heads with zeros up to it), or 0."""
+    for hd in (64, 128, 256):
+        if hd >= size and (_lib().af_attn_prefill_tc_supported(c_int(hd)) or _lib().af_attn_prefill_supported(c_int(hd))):
+            return hd
+    return 0
+
+
 def latent_prep(q, kvrow, proj, batch, heads: int, dim: int, rot: int, rank: int, norm_w, eps: float, inv_freq,
-                kv=None) -> None:
+                kv=None, pitch: int = 0) -> None:
     """From float32 projection rows [q heads of (dim + rot) | latent of ``rank`` | shared key part of ``rot``]:
-    the q heads with their last ``rot`` elements rotated (pairs i, i + rot / 2) into ``q`` [T, heads (dim + rot)];
+    the q heads with their last ``rot`` elements rotated (pairs i, i + rot / 2) into ``q`` [T, heads pitch]
+    (``pitch`` >= dim + rot, by default that: a head's elements beyond dim + rot are set to zero);
     the latent over its root mean square (eps inside the root) times ``norm_w`` and the rotated shared key part
     into ``kvrow`` [T, rank + rot], and, with ``kv`` (the layer's view of its cache: one kv head of rank + rot
     elements, no value pages), into each token's row of its page."""
     T = proj.shape[0]
-    if proj.shape[1] < heads * (dim + rot) + rank + rot or tuple(q.shape) != (T, heads * (dim + rot)) \
+    pitch = pitch or dim + rot
+    if proj.shape[1] < heads * (dim + rot) + rank + rot or tuple(q.shape) != (T, heads * pitch) \
             or tuple(kvrow.shape) != (T, rank + rot) or q.dtype != kvrow.dtype:
         raise KernelError("latent_prep: shapes of the projection, q and kv rows do not fit")
     if inv_freq.numel() != rot // 2 or norm_w.numel() != rank:
@@ -953,7 +969,7 @@ def latent_prep(q, kvrow, proj, batch, heads: int, dim: int, rot: int, rank: int
         pp, ld, _ptr(norm_w, "norm_w", torch.float32), c_float(eps), _ptr(batch.positions, "positions", torch.int32),
         _ptr(batch.seq_of_token, "seq_of_token", torch.int32), _ptr(batch.slots, "slots", torch.int32),
         _ptr(batch.len_after, "len_after", torch.int32), _ptr(inv_freq, "inv_freq", torch.float32), c_int(T),
-        c_int(heads), c_int(dim), c_int(rot), c_int(rank), _ptr(kc, allow_none=True),
+        c_int(heads), c_int(dim), c_int(rot), c_int(rank), c_int(pitch), _ptr(kc, allow_none=True),
         _ptr(pt, "page_table", torch.int32, allow_none=True), c_int(max_pages), c_int(ring), _stream()))
 
 

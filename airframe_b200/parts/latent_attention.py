@@ -16,6 +16,13 @@ W_uv,a (sum_j p_j c_j).  The attention itself then runs over one shared
 key/value head whose key row is the cached [c | r] (``kv_rank + rot_dim``
 elements) and whose value is the first ``kv_rank`` elements of the same row;
 the cache holds no value pages.
+
+A prompt in bfloat16 goes the other way round where the head sizes allow: one
+product turns the step's rows [c | r] into every head's key [W_uk,a c | r] and
+value W_uv,a c (the weight holds W_uk, W_uv and an identity for r, heads padded
+with zeros up to a size the tensor-core attention kernels take), and those
+kernels run as for ordinary heads; per token that costs a product with W_uk and
+W_uv once, not once per key it sees.
 """
 from __future__ import annotations
 
@@ -65,6 +72,8 @@ class LatentAttention(Mixer):
                                                  "o_weight")}
         self.sink_name = self.params.get("sink_weight")
         self.w_in = self.w_uk = self.w_uv = self.w_o = self.norm_w = self.sinks = None
+        self.fast_hd = 0            # head size of the prompt's tensor-core path (0: there is none)
+        self.w_up = self.w_o_fast = None
 
     def kv_need(self):
         return KVNeed(1, self.rank + self.rot, self.window, 0)       # (values: the latent part of the key row)
@@ -93,6 +102,24 @@ class LatentAttention(Mixer):
         if self.sink_name:
             self.sinks = weights[self.sink_name].to(torch.float32).contiguous()
         self.position.load(weights)
+        # a prompt's path over the tensor-core attention kernels: keys and values of every head out of one product
+        hd = 0
+        if dt == torch.bfloat16 and self.w_o.is_cuda and (self.rank + self.rot) % 8 == 0 and self.mask == "window":
+            hd = kernels.attn_prefill_fast_head(max(self.dim + self.rot, self.dv))
+        if hd:
+            up = torch.zeros(2 * H * hd, self.rank + self.rot, dtype=dt, device=self.w_o.device)
+            k_rows, v_rows = up[: H * hd].view(H, hd, -1), up[H * hd:].view(H, hd, -1)
+            k_rows[:, : self.dim, : self.rank] = weights[n["uk_weight"]].to(dt).view(H, self.dim, self.rank)
+            k_rows[:, self.dim: self.dim + self.rot, self.rank:] = torch.eye(self.rot, dtype=dt, device=up.device)
+            v_rows[:, : self.dv, : self.rank] = weights[n["uv_weight"]].to(dt).view(H, self.dv, self.rank)
+            self.w_up = up
+            if hd == self.dv:
+                self.w_o_fast = self.w_o
+            else:
+                wide = torch.zeros(self.hidden, H, hd, dtype=dt, device=up.device)
+                wide[:, :, : self.dv] = self.w_o.view(self.hidden, H, self.dv)
+                self.w_o_fast = wide.view(self.hidden, H * hd).contiguous()
+            self.fast_hd = hd
 
     def _el(self) -> int:
         return 4 if self.ctx.compute_dtype == torch.float32 else 2
@@ -116,6 +143,8 @@ class LatentAttention(Mixer):
                 pairs += full * (w * (w + 1) // 2) + rest * (rest + 1) // 2
             else:
                 pairs += n * (n + 1) // 2 if not w or n <= w else w * (w + 1) // 2 + (n - w) * w
+        if self.fast_hd:        # (a prompt's path: ordinary heads of dim + rot key and value_dim value elements)
+            return 2 * pairs * self.heads * (self.dim + self.rot + self.dv)
         return 2 * pairs * self.heads * (2 * self.rank + self.rot)
 
     def prefill_flops(self, lens) -> int:
@@ -123,10 +152,33 @@ class LatentAttention(Mixer):
         proj = 2 * T * (self.w_in.numel() + self.w_uk.numel() + self.w_uv.numel() + self.w_o.numel())
         return proj + self.score_flops(lens)
 
+    FAST_PROMPT_ROWS = 64      # from this many rows on a bfloat16 prompt takes the tensor-core path
+
+    def _prompt_on_tensor_cores(self, proj, batch, view):
+        """Keys and values of every head from the step's latent rows by one product, then the attention kernels
+        of ordinary heads (a window, a sink)."""
+        H, hd = self.heads, self.fast_hd
+        T, dt, dev = proj.shape[0], self.ctx.compute_dtype, proj.device
+        q = torch.empty(T, H * hd, dtype=dt, device=dev)
+        kvrow = torch.empty(T, self.rank + self.rot, dtype=dt, device=dev)
+        kernels.latent_prep(q, kvrow, proj, batch, H, self.dim, self.rot, self.rank, self.norm_w, self.eps,
+                            self.position.inv_freq, kv=view.kv if view.writes else None, pitch=hd)
+        if not view.writes:
+            kvrow = batch.step_kv[view.cache_id][0]
+        elif view.keep_step_kv:
+            batch.step_kv[view.cache_id] = (kvrow, kvrow[:, : self.rank])
+        kv_up = linear(kvrow, self.w_up)
+        ctx = torch.empty(T, H * hd, dtype=dt, device=dev)
+        kernels.attn_prefill(ctx, q, kv_up[:, : H * hd], kv_up[:, H * hd:], batch, H, H, hd, self.scale, 0.0,
+                             self.window or 0, mask=self.mask, sinks=self.sinks)
+        return linear_split(ctx, self.w_o_fast, wide=bool(self.params.get("wide_output", False)))
+
     def forward(self, x, batch, view):
         H, dim, rot, rank, dv = self.heads, self.dim, self.rot, self.rank, self.dv
         T, dt = x.shape[0], x.dtype
         proj = linear(x, self.w_in, out_dtype=torch.float32)
+        if batch.is_prefill and self.fast_hd and T >= self.FAST_PROMPT_ROWS:
+            return self._prompt_on_tensor_cores(proj, batch, view)
         q = torch.empty(T, H * (dim + rot), dtype=dt, device=x.device)
         kvrow = torch.empty(T, rank + rot, dtype=dt, device=x.device)
         kernels.latent_prep(q, kvrow, proj, batch, H, dim, rot, rank, self.norm_w, self.eps, self.position.inv_freq,
