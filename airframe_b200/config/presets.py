@@ -55,7 +55,7 @@ def _banitar_small() -> dict:
     """Banitar with four layers, the two in the middle run twice (sizes of no released model)."""
     attn = {"heads": 8, "kv_heads": 2, "dim": 64, "vdim": 64, "mask": {"size": 256}, "scale": 0.125,
             "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 512, "fast": 32.0, "slow": 1.0}}}
-    latent = {"heads": 8, "dim": 32, "rot_dim": 32, "vdim": 64, "kv_rank": 128, "mask": {"size": 192}, "scale": 0.125,
+    latent = {"heads": 8, "dim": 32, "rot_dim": 32, "vdim": 64, "kv_rank": 96, "mask": {"size": 192}, "scale": 0.125,
               "rot": {"base": 10000.0, "dims": 32}}
     layers = [{"type": "attention", "mixer": attn, "mlp": {"kind": "dense", "ff": 1536}},
               {"type": "latent_attention", "mixer": latent, "mlp": {"kind": "dense", "ff": 1536}},

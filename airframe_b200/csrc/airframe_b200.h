@@ -25,6 +25,15 @@ int af_attn_decode(void* out, long long out_stride, const void* q, long long q_s
                    const int* lens, int batch, int nq, int nkv, int hd, float scale, float cap, int window,
                    int ring_rows, int n_splits, float* scratch, const int* plan, int* err, cudaStream_t stream);
 
+// The same with a learned sink per head (float [nq] on the device, or null): exp(sink) joins the head's softmax
+// denominator without a key or a value.  `window` < 0 (here and above): the token sees its own chunk of -window
+// positions, chunks counted from position 0, instead of the last `window` positions.
+int af_attn_decode_sinks(void* out, long long out_stride, const void* q, long long q_stride, const void* kcache,
+                         const void* vcache, long long n_pages, const int* page_table, int max_pages, const int* slots,
+                         const int* lens, int batch, int nq, int nkv, int hd, float scale, float cap, int window,
+                         int ring_rows, int n_splits, float* scratch, const int* plan, const float* sinks, int* err,
+                         cudaStream_t stream);
+
 // The plan of a step: how af_attn_decode cuts its work, made once for all layers that read the same caches the
 // same way.  `plan`: af_attn_decode_plan_ints(...) 32-bit integers of device memory, 16-byte aligned.
 long long af_attn_decode_plan_ints(int batch, int nq, int nkv);

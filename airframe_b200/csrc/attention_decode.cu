@@ -75,6 +75,7 @@ struct DecodeArgs {
   const int* plan; // the step's plan (attn_decode_plan_kernel), or null: every block works the cut out itself
   __nv_bfloat16* out;  // [batch, nq * HD], rows out_stride apart
   long long out_stride;
+  const float* sinks;  // [nq] or null: exp(sink) joins a head's softmax denominator (no key, no value)
 };
 
 __device__ __forceinline__ void da_ldm4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
@@ -747,9 +748,11 @@ __global__ void attn_decode_merge_kernel(__nv_bfloat16* __restrict__ out, long l
                                          const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          int nq, int nkv, int max_splits, const int* __restrict__ slots,
                                          const int* __restrict__ lens, int window, int grid_blocks,
-                                         const int* __restrict__ plan) {
+                                         const int* __restrict__ plan, const float* __restrict__ sinks) {
   pdl_launch_dependents();
   const int b = blockIdx.x, h = blockIdx.y, batch = gridDim.x;
+  // (the splits' maxima are base-2 exponents: the sink, a natural one, is brought there; a weight, not a result)
+  const float sink2 = sinks ? sinks[h] * 1.4426950408889634f : -INFINITY;
   const size_t p0 = ((size_t)b * nq + h) * max_splits;
   __shared__ DaPlan plan_s;
   __shared__ float m_sh[DA_MERGE_MOST], l_sh[DA_MERGE_MOST];
@@ -810,6 +813,7 @@ __global__ void attn_decode_merge_kernel(__nv_bfloat16* __restrict__ out, long l
 #pragma unroll
       for (int e = 0; e < PER; ++e) O[e] += o[s][e] * f;
     }
+    if (sinks) L += exp2f(sink2 - ref);
     const float inv = L > 0.f ? 1.f / L : 0.f;
 #pragma unroll
     for (int e = 0; e < PER; ++e) dst[d + e * 128] = __float2bfloat16_rn(O[e] * inv);
@@ -834,6 +838,7 @@ __global__ void attn_decode_merge_kernel(__nv_bfloat16* __restrict__ out, long l
     for (int s = tid & 31; s < n_splits; s += 32) L += l_sh[s] * fast_exp2(m_sh[s] - ref);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+    if (sinks) L += exp2f(sink2 - ref);
     constexpr int ROW = HD / 2;                       // threads of a group
     const int GROUPS = (int)blockDim.x / ROW;         // (1 .. 16)
     const int grp = tid / ROW, dp = tid - grp * ROW;
@@ -883,6 +888,7 @@ __global__ void attn_decode_merge_kernel(__nv_bfloat16* __restrict__ out, long l
   const float ref = M == -INFINITY ? 0.f : M;
   float L = 0.f;
   for (int s = 0; s < n_splits; ++s) L += part_ml[(p0 + s) * 2 + 1] * fast_exp2(part_ml[(p0 + s) * 2] - ref);
+  if (sinks) L += exp2f(sink2 - ref);
   const float inv = L > 0.f ? 1.f / L : 0.f;
   for (int dd = threadIdx.x; dd < HD; dd += blockDim.x) {
     float O = 0.f;
@@ -927,7 +933,7 @@ int launch_decode(DecodeArgs a, int batch, long long n_pages, cudaStream_t strea
   const int merge_threads = a.n_splits > DA_MERGE_FEW && batch * a.nq <= 32 ? DA_MERGE_THREADS : (HD < 128 ? HD : 128);
   af_launch(attn_decode_merge_kernel<HD>, dim3(batch, a.nq), dim3(merge_threads), 0, stream, a.out, a.out_stride,
             (const float*)a.part_o, (const float*)a.part_ml, a.nq, a.nkv, a.n_splits, a.slots, a.lens, a.window,
-            n_blocks, a.plan);
+            n_blocks, a.plan, a.sinks);
   AF_CHECK_LAUNCH("af_attn_decode (merge)");
 }
 
@@ -946,7 +952,7 @@ AF_EXPORT long long af_attn_decode_scratch(int batch, int nq, int hd, int n_spli
 // The cache of the layer holds n_pages pages [kv heads][64][hd].  scratch:
 // af_attn_decode_scratch(...) floats.  Sequences with slot < 0 give zeros.  n_splits: the most splits
 // of a sequence's keys (the third extent of the grid).
-AF_EXPORT int af_attn_decode(void* out, long long out_stride, const void* q, long long q_stride,
+static int attn_decode_impl(const float* sinks, void* out, long long out_stride, const void* q, long long q_stride,
                              const void* kcache, const void* vcache, long long n_pages, const int* page_table,
                              int max_pages, const int* slots, const int* lens, int batch, int nq, int nkv, int hd,
                              float scale, float cap, int window, int ring_rows, int n_splits, float* scratch,
@@ -984,10 +990,31 @@ AF_EXPORT int af_attn_decode(void* out, long long out_stride, const void* q, lon
   a.plan = plan;
   a.out = (__nv_bfloat16*)out;
   a.out_stride = out_stride;
+  a.sinks = sinks;
   AF_REQUIRE(n_pages > 0 && n_pages * nkv * AF_PAGE < (1ll << 31), "af_attn_decode: %lld cache pages", n_pages);
   if (hd == 64) return launch_decode<64>(a, batch, n_pages, stream);
   if (hd == 128) return launch_decode<128>(a, batch, n_pages, stream);
   return launch_decode<256>(a, batch, n_pages, stream);
+}
+
+AF_EXPORT int af_attn_decode(void* out, long long out_stride, const void* q, long long q_stride, const void* kcache,
+                             const void* vcache, long long n_pages, const int* page_table, int max_pages,
+                             const int* slots, const int* lens, int batch, int nq, int nkv, int hd, float scale,
+                             float cap, int window, int ring_rows, int n_splits, float* scratch, const int* plan,
+                             int* err, cudaStream_t stream) {
+  return attn_decode_impl(nullptr, out, out_stride, q, q_stride, kcache, vcache, n_pages, page_table, max_pages, slots,
+                          lens, batch, nq, nkv, hd, scale, cap, window, ring_rows, n_splits, scratch, plan, err, stream);
+}
+
+// The same with a learned sink per head (float [nq], or null): exp(sink) joins the head's softmax denominator
+// without a key or a value.
+AF_EXPORT int af_attn_decode_sinks(void* out, long long out_stride, const void* q, long long q_stride,
+                                   const void* kcache, const void* vcache, long long n_pages, const int* page_table,
+                                   int max_pages, const int* slots, const int* lens, int batch, int nq, int nkv, int hd,
+                                   float scale, float cap, int window, int ring_rows, int n_splits, float* scratch,
+                                   const int* plan, const float* sinks, int* err, cudaStream_t stream) {
+  return attn_decode_impl(sinks, out, out_stride, q, q_stride, kcache, vcache, n_pages, page_table, max_pages, slots,
+                          lens, batch, nq, nkv, hd, scale, cap, window, ring_rows, n_splits, scratch, plan, err, stream);
 }
 
 // ---------------------------------------------------------------- the plan of a step

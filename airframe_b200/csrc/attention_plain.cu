@@ -811,18 +811,19 @@ AF_EXPORT int af_latent_prep(void* q, long long q_stride, void* kv, long long kv
 // ---------------------------------------------------------------- a small product per head
 
 // out[t, h, n] = sum_d x[t, h, d] * w[h, d, n] for d < D, n < N (32-bit sums in index order), and the
-// `extra` elements that follow a head's D inputs copied behind its N outputs.  x rows: heads of
-// (D + extra) elements, `x_stride` apart; out rows: heads of (N + extra), `out_stride` apart; w [heads, D, N].
+// `extra` elements that follow a head's D inputs copied behind its N outputs.  x rows: heads `x_pitch`
+// elements apart (at least D + extra), rows `x_stride` apart; out rows: heads of (N + extra), `out_stride` apart;
+// w [heads, D, N].
 // One block per (token, head); the head's inputs wait in shared memory.
 template <typename T>
 __global__ void __launch_bounds__(256)
 head_project_kernel(T* __restrict__ out, long long out_stride, const T* __restrict__ x, long long x_stride,
-                    const T* __restrict__ w, int D, int N, int extra) {
+                    const T* __restrict__ w, int D, int N, int extra, int x_pitch) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float xs[];
   const int t = blockIdx.x, h = blockIdx.y;
-  const T* xr = x + (size_t)t * x_stride + (size_t)h * (D + extra);
+  const T* xr = x + (size_t)t * x_stride + (size_t)h * x_pitch;
   T* o = out + (size_t)t * out_stride + (size_t)h * (N + extra);
   for (int d = threadIdx.x; d < D; d += blockDim.x) xs[d] = to_f32(xr[d]);
   for (int e = threadIdx.x; e < extra; e += blockDim.x) o[N + e] = xr[D + e];
@@ -836,13 +837,15 @@ head_project_kernel(T* __restrict__ out, long long out_stride, const T* __restri
 }
 
 AF_EXPORT int af_head_project(void* out, long long out_stride, const void* x, long long x_stride, const void* w,
-                              int dtype, int n_tokens, int heads, int D, int N, int extra, cudaStream_t stream) {
+                              int dtype, int n_tokens, int heads, int D, int N, int extra, int x_pitch,
+                              cudaStream_t stream) {
   if (n_tokens == 0) return 0;
-  AF_REQUIRE(n_tokens > 0 && heads > 0 && heads < 65536 && D > 0 && N > 0 && extra >= 0, "af_head_project: bad sizes");
+  AF_REQUIRE(n_tokens > 0 && heads > 0 && heads < 65536 && D > 0 && N > 0 && extra >= 0 && x_pitch >= D + extra,
+             "af_head_project: bad sizes");
   AF_REQUIRE((size_t)D * sizeof(float) <= 48 * 1024, "af_head_project: %d inputs a head beyond 12288", D);
   const int threads = N >= 256 ? 256 : ((N + 31) / 32) * 32;
   AF_DISPATCH_DTYPE(dtype, T,
                     af_launch(head_project_kernel<T>, dim3(n_tokens, heads), dim3(threads), (size_t)D * sizeof(float),
-                              stream, (T*)out, out_stride, (const T*)x, x_stride, (const T*)w, D, N, extra));
+                              stream, (T*)out, out_stride, (const T*)x, x_stride, (const T*)w, D, N, extra, x_pitch));
   AF_CHECK_LAUNCH("af_head_project");
 }

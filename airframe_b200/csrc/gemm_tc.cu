@@ -71,7 +71,11 @@ __device__ __forceinline__ float tc_act(float g, int act) {
     asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
     return 0.5f * g * (1.f + t);
   }
-  return g / (1.f + __expf(-g));
+  // SiLU: g * sigmoid(g) with sigmoid(g) = (1 + tanh(g / 2)) / 2, one special-function operation as the GELU above
+  // (an exponential and a division cost the epilogue warps half as much again as the whole GELU)
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * g));
+  return 0.5f * g * (1.f + t);
 }
 
 struct TcArgs {

@@ -721,7 +721,7 @@ def attn_decode_plan(page_table, slots, lens, nq: int, nkv: int, window: int, ri
 
 
 def attn_decode_split(out, q, kcache, vcache, page_table, slots, lens, nq, nkv, hd, scale, cap, window, ring_rows,
-                      n_splits: int, scratch=None, plan=None) -> None:
+                      n_splits: int, scratch=None, plan=None, sinks=None) -> None:
     """bfloat16 decode attention, split over the keys (two kernels: partial
     results into ``scratch``, then their merge).  ``n_splits`` is the most
     splits a (sequence, kv head) unit gets: the kernel cuts the units' pages so
@@ -737,17 +737,25 @@ def attn_decode_split(out, q, kcache, vcache, page_table, slots, lens, nq, nkv, 
         raise KernelError(f"attn_decode_split: scratch of {need} floats wanted")
     if q.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("attn_decode_split: bfloat16 only")
-    _check(lib.af_attn_decode(
+    if sinks is not None and sinks.numel() != nq:
+        raise KernelError(f"attn_decode_split: {sinks.numel()} sinks for {nq} heads")
+    _check(lib.af_attn_decode_sinks(
         _ptr(out), c_longlong(_rows(out, "out")), _ptr(q), c_longlong(_rows(q, "q")), _ptr(kcache), _ptr(vcache),
         c_longlong(kcache.shape[0]), _ptr(page_table, "page_table", torch.int32), c_int(page_table.shape[1]),
         _ptr(slots, "slots", torch.int32),
         _ptr(lens, "lens", torch.int32), c_int(B), c_int(nq), c_int(nkv), c_int(hd), c_float(scale), c_float(cap),
         c_int(window), c_int(ring_rows), c_int(n_splits), _ptr(scratch, "scratch", torch.float32),
         _ptr(plan, "plan", torch.int32) if plan is not None else ctypes.c_void_p(0),
+        _ptr(sinks, "sinks", torch.float32, allow_none=True),
         _ptr(error_word(q.device), "err", torch.int32), _stream()))
 
 
 ATTN_DECODE_MAX_SEQS = 2048     # sequences of a step that the split kernel plans for (more: the plain kernel)
+
+
+def attn_decode_fast(dtype, hd: int, n_seqs: int) -> bool:
+    """Whether :func:`attn_decode` has the split kernel for these sizes."""
+    return dtype == torch.bfloat16 and bool(_lib().af_attn_decode_supported(c_int(hd))) and n_seqs <= ATTN_DECODE_MAX_SEQS
 
 
 def attn_decode(out, q, kv, batch, nq, nkv, hd, scale, cap, window, slopes=None, dv=None, mask: str = "window",
@@ -756,7 +764,10 @@ def attn_decode(out, q, kv, batch, nq, nkv, hd, scale, cap, window, slopes=None,
     bfloat16 and head sizes it takes (a chunked mask goes to it as a negative window, a gate follows it as a
     kernel of its own), else the plain kernel (which also serves scores with a per-head slope, values of another
     size than the keys or inside them, and sinks)."""
-    special = slopes is not None or (dv or hd) != hd or kv.v is None or sinks is not None
+    # values that lie inside their key rows: the split kernel takes the key pages for the value pages too and gives
+    # whole key-sized rows back, of which the caller (who asked for it with an `out` that wide) reads the values' part
+    wide = kv.v is None and out.shape[1] == nq * hd
+    special = slopes is not None or (not wide and ((dv or hd) != hd or kv.v is None))
     if (not special and q.dtype == torch.bfloat16 and _lib().af_attn_decode_supported(c_int(hd))
             and batch.n_seqs <= ATTN_DECODE_MAX_SEQS):
         if mask == "chunk":
@@ -771,8 +782,8 @@ def attn_decode(out, q, kv, batch, nq, nkv, hd, scale, cap, window, slopes=None,
                 aux[key] = attn_decode_plan(kv.page_table, batch.slots, batch.len_after, nq, nkv, window,
                                             kv.ring_rows, n)
             plan = aux[key]
-        attn_decode_split(out, q, kv.k, kv.v, kv.page_table, batch.slots, batch.len_after, nq, nkv, hd, scale, cap,
-                          window, kv.ring_rows, n, plan=plan)
+        attn_decode_split(out, q, kv.k, kv.k if wide else kv.v, kv.page_table, batch.slots, batch.len_after, nq, nkv,
+                          hd, scale, cap, window, kv.ring_rows, n, plan=plan, sinks=sinks)
         if gate is not None:
             head_gate(out, gate, nq, hd)
         return
@@ -973,17 +984,18 @@ def latent_prep(q, kvrow, proj, batch, heads: int, dim: int, rot: int, rank: int
         _ptr(pt, "page_table", torch.int32, allow_none=True), c_int(max_pages), c_int(ring), _stream()))
 
 
-def head_project(out, x, w, heads: int, D: int, N: int, extra: int = 0) -> None:
+def head_project(out, x, w, heads: int, D: int, N: int, extra: int = 0, x_pitch: int = 0) -> None:
     """out[t, h, :N] = x[t, h, :D] @ w[h] for w [heads, D, N] (32-bit sums), and the ``extra`` elements behind a
-    head's D inputs copied behind its N outputs.  x [T, heads (D + extra)], out [T, heads (N + extra)]: row views
-    of one dtype, which is w's too."""
+    head's D inputs copied behind its N outputs.  x [T, heads x_pitch] (``x_pitch`` = D + extra by default: what
+    else a head holds is skipped), out [T, heads (N + extra)]: row views of one dtype, which is w's too."""
     T = x.shape[0]
-    if tuple(x.shape) != (T, heads * (D + extra)) or tuple(out.shape) != (T, heads * (N + extra)) \
+    x_pitch = x_pitch or D + extra
+    if tuple(x.shape) != (T, heads * x_pitch) or tuple(out.shape) != (T, heads * (N + extra)) \
             or tuple(w.shape) != (heads, D, N) or not w.is_contiguous() or not (x.dtype == out.dtype == w.dtype):
         raise KernelError("head_project: shapes or dtypes do not fit")
     _check(_lib().af_head_project(_ptr(out), c_longlong(_rows(out, "out")), _ptr(x), c_longlong(_rows(x, "x")), _ptr(w),
                                   c_int(dtype_code(x.dtype)), c_int(T), c_int(heads), c_int(D), c_int(N), c_int(extra),
-                                  _stream()))
+                                  c_int(x_pitch), _stream()))
 
 
 # ---------------------------------------------------------------- the norm without statistics, and re-entry

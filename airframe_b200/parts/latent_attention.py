@@ -186,7 +186,10 @@ class LatentAttention(Mixer):
         # the queries on the latent's side: [W_uk^T q_plain | q_rot] per head
         q_lat = torch.empty(T, H * (rank + rot), dtype=dt, device=x.device)
         kernels.head_project(q_lat, q, self.w_uk, H, dim, rank, extra=rot)
-        mix = torch.empty(T, H * rank, dtype=dt, device=x.device)
+        # a decode step whose key rows have a size the split kernel takes gets whole rows [sum p c | sum p r] back
+        # from it (the key pages serve as value pages); the values' part is read from there
+        wide = not batch.is_prefill and kernels.attn_decode_fast(dt, rank + rot, batch.n_seqs)
+        mix = torch.empty(T, H * (rank + rot if wide else rank), dtype=dt, device=x.device)
         window = self.window or 0
         if batch.is_prefill:
             if not view.writes:
@@ -200,5 +203,5 @@ class LatentAttention(Mixer):
                                 mask=self.mask, sinks=self.sinks)
         # back from the latent to the heads' values, then the output projection
         ctx = torch.empty(T, H * dv, dtype=dt, device=x.device)
-        kernels.head_project(ctx, mix, self.w_uv, H, rank, dv)
+        kernels.head_project(ctx, mix, self.w_uv, H, rank, dv, x_pitch=rank + rot if wide else rank)
         return linear_split(ctx, self.w_o, wide=bool(self.params.get("wide_output", False)))

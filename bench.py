@@ -506,10 +506,10 @@ def _banitar_sizes(width, layers, heads, kv_heads, attn_dim, lat_dim, rot_dim, v
 
 
 BANITAR_POINTS = {
-    "w1024": dict(width=1024, layers=8, heads=16, kv_heads=4, attn_dim=64, lat_dim=32, rot_dim=32, vdim=64, kv_rank=128,
+    "w1024": dict(width=1024, layers=8, heads=16, kv_heads=4, attn_dim=64, lat_dim=32, rot_dim=32, vdim=64, kv_rank=96,
                   window=1024, ff=4096, vocab=32000),
     "w2304": dict(width=2304, layers=8, heads=18, kv_heads=6, attn_dim=128, lat_dim=64, rot_dim=64, vdim=128,
-                  kv_rank=256, window=4096, ff=9216, vocab=32000),
+                  kv_rank=192, window=4096, ff=9216, vocab=32000),
     "w4096": dict(width=4096, layers=8, heads=32, kv_heads=8, attn_dim=128, lat_dim=64, rot_dim=64, vdim=128,
                   kv_rank=512, window=4096, ff=14336, vocab=32000),
     # a latent head whose key (128 + 64) and value (128) sizes differ

@@ -48,7 +48,7 @@ BN_B = {
         _layer("attention", _attn(6, 2, 64, 64, 70, 32, 10000.0, 0.125, {"factor": 8.0, "original": 64, "fast": 16.0,
                                                                          "slow": 2.0}), ff=256),
         _layer("latent_attention", _latent(4, 32, 32, 64, 64, 130, 500.0, 0.2), ff=192),
-        _layer("latent_attention", _latent(2, 64, 16, 32, 96, 33, 1e6, 0.1)),
+        _layer("latent_attention", _latent(2, 64, 16, 32, 112, 33, 1e6, 0.1)),     # (cached rows of 128: the split decode kernel)
         _layer("attention", _attn(2, 2, 64, 32, 128, 64, 500.0, 0.2), ff=160),
     ],
     "loop": {"start": 1, "stop": 3, "times": 3},
@@ -60,7 +60,7 @@ BN_C = {
     "architecture": "Banitar", "vocab": 500, "width": 256, "embedding": {"scale": 0.5}, "norm": {"eps": 1e-6},
     "layers": [
         _layer("attention", _attn(4, 1, 128, 128, 100, 128, 30000.0, 0.09), ff=320),
-        _layer("latent_attention", _latent(4, 64, 64, 128, 128, 1, 1e4, 0.09)),
+        _layer("latent_attention", _latent(4, 64, 64, 128, 192, 1, 1e4, 0.09)),    # (cached rows of 256)
         _layer("attention", _attn(2, 1, 128, 64, 1, 64, 1e5, 0.1), ff=256),
         _layer("latent_attention", _latent(2, 128, 64, 128, 256, 80, 1e4, 0.07), ff=128),
     ],
