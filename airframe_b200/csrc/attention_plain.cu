@@ -491,20 +491,40 @@ attn_decode_plain_merge_kernel(T* __restrict__ out, int out_stride, const float*
   const int b = blockIdx.x, h = blockIdx.y;
   if (slots[b] < 0) return;                                  // (a padding row: the split kernel wrote zeros)
   const size_t u = ((size_t)b * nq + h) * n_splits;
-  float M = sinks ? sinks[h] : -INFINITY;
-  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[2 * (u + s)]);
-  float L = sinks ? expf(sinks[h] - M) : 0.f;
-  for (int s = 0; s < n_splits; ++s) {
-    const float m = part_ml[2 * (u + s)];
-    if (m > -INFINITY) L += part_ml[2 * (u + s) + 1] * expf(m - M);
+  // every run's factor e^(m_s - M) / L once, in shared memory (up to 256 runs; more: worked out again by every thread)
+  __shared__ float f_s[256];
+  __shared__ float inv_s;
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    float M = sinks ? sinks[h] : -INFINITY;
+    for (int s = lane; s < n_splits; s += 32) M = fmaxf(M, part_ml[2 * (u + s)]);
+    M = warp_max(M);
+    float L = 0.f;
+    for (int s = lane; s < n_splits; s += 32) {
+      const float m = part_ml[2 * (u + s)];
+      const float f = m > -INFINITY ? expf(m - M) : 0.f;
+      if (s < 256) f_s[s] = f;
+      L += part_ml[2 * (u + s) + 1] * f;
+    }
+    L = warp_sum(L);
+    if (sinks) L += expf(sinks[h] - M);
+    if (lane == 0) inv_s = L > 0.f ? gate_factor(gate, gate_stride, b, h) / L : 0.f;
+    if (n_splits > 256 && lane == 0) f_s[0] = M;       // (kept for the long way below)
   }
-  const float inv = L > 0.f ? gate_factor(gate, gate_stride, b, h) / L : 0.f;
+  __syncthreads();
+  const float inv = inv_s;
   T* o = out + (size_t)b * out_stride + (size_t)h * dv;
   for (int d = threadIdx.x; d < dv; d += blockDim.x) {
     float acc = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-      const float m = part_ml[2 * (u + s)];
-      if (m > -INFINITY) acc += part_o[(u + s) * dv + d] * expf(m - M);
+    if (n_splits <= 256) {
+#pragma unroll 4
+      for (int s = 0; s < n_splits; ++s) acc += part_o[(u + s) * dv + d] * f_s[s];
+    } else {
+      const float M = f_s[0];
+      for (int s = 0; s < n_splits; ++s) {
+        const float m = part_ml[2 * (u + s)];
+        if (m > -INFINITY) acc += part_o[(u + s) * dv + d] * expf(m - M);
+      }
     }
     o[d] = from_f32<T>(acc * inv);
   }
@@ -546,6 +566,19 @@ AF_EXPORT int af_attn_decode_plain(void* out, int out_stride, const void* q, int
                               out_stride, (const float*)part_o, (const float*)part_ml, slots, nq, dv, n_splits, sinks,
                               gate, gate_stride));
   AF_CHECK_LAUNCH("af_attn_decode_plain");
+}
+
+// The merge alone, for kernels that leave runs in the same form (attention_latent.cu).
+AF_EXPORT int af_attn_decode_merge_runs(void* out, int out_stride, int dtype, const float* part_o, const float* part_ml,
+                                        const int* slots, int batch, int nq, int dv, int n_splits, const float* sinks,
+                                        const float* gate, long long gate_stride, cudaStream_t stream) {
+  if (batch == 0) return 0;
+  AF_REQUIRE(batch > 0 && batch < 65536 && nq > 0 && nq < 65536 && dv > 0 && n_splits >= 1 && part_o && part_ml,
+             "af_attn_decode_merge_runs: bad sizes");
+  AF_DISPATCH_DTYPE(dtype, T,
+                    af_launch(attn_decode_plain_merge_kernel<T>, dim3(batch, nq), dim3(128), 0, stream, (T*)out,
+                              out_stride, part_o, part_ml, slots, nq, dv, n_splits, sinks, gate, gate_stride));
+  AF_CHECK_LAUNCH("af_attn_decode_merge_runs");
 }
 
 // An output gate behind an attention kernel that has none of its own: x[t, h, :] *= sigmoid(gate[t, h]).
@@ -726,7 +759,7 @@ AF_EXPORT int af_qk_norm_rope_store(void* qkv, int dtype, long long out_stride, 
 //   page (one kv head of rank + rot elements; the values are the latent part of the same row).
 // One block per token.
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 latent_prep_kernel(T* __restrict__ q, long long q_stride, T* __restrict__ kv, long long kv_stride,
                    const float* __restrict__ proj, long long ld, const float* __restrict__ norm_w, float eps,
                    const int* __restrict__ positions, const int* __restrict__ seq_of_token,
@@ -802,7 +835,7 @@ AF_EXPORT int af_latent_prep(void* q, long long q_stride, void* kv, long long kv
              pitch >= dim + rot, "af_latent_prep: bad sizes");
   AF_REQUIRE(ring_rows % AF_PAGE == 0, "af_latent_prep: ring rows %d not whole pages", ring_rows);
   AF_DISPATCH_DTYPE(dtype, T,
-                    af_launch(latent_prep_kernel<T>, dim3(n_tokens), dim3(128), 0, stream, (T*)q, q_stride, (T*)kv,
+                    af_launch(latent_prep_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, (T*)q, q_stride, (T*)kv,
                               kv_stride, proj, ld, norm_w, eps, positions, seq_of_token, slots, len_after, inv_freq,
                               heads, dim, rot, rank, pitch, (T*)kcache, page_table, max_pages, ring_rows));
   AF_CHECK_LAUNCH("af_latent_prep");
@@ -810,18 +843,21 @@ AF_EXPORT int af_latent_prep(void* q, long long q_stride, void* kv, long long kv
 
 // ---------------------------------------------------------------- a small product per head
 
-// out[t, h, n] = sum_d x[t, h, d] * w[h, d, n] for d < D, n < N (32-bit sums in index order), and the
+// out[t, h, n] = sum_d x[t, h, d] * w[h, d, n] for d < D, n < N (32-bit sums), and the
 // `extra` elements that follow a head's D inputs copied behind its N outputs.  x rows: heads `x_pitch`
 // elements apart (at least D + extra), rows `x_stride` apart; out rows: heads of (N + extra), `out_stride` apart;
 // w [heads, D, N].
-// One block per (token, head); the head's inputs wait in shared memory.
+// One block of 256 threads per (token, head); the head's inputs wait in shared memory.  With fewer than 256
+// outputs the threads form 256 / cols groups that each take a stretch of the inputs (a long sum is then several
+// short chains side by side); the groups' sums are added in group order.
 template <typename T>
 __global__ void __launch_bounds__(256)
 head_project_kernel(T* __restrict__ out, long long out_stride, const T* __restrict__ x, long long x_stride,
-                    const T* __restrict__ w, int D, int N, int extra, int x_pitch) {
+                    const T* __restrict__ w, int D, int N, int extra, int x_pitch, int cols) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ float xs[];
+  extern __shared__ float xs[];                     // D inputs, then [groups][cols] partial sums
+  float* red = xs + D;
   const int t = blockIdx.x, h = blockIdx.y;
   const T* xr = x + (size_t)t * x_stride + (size_t)h * x_pitch;
   T* o = out + (size_t)t * out_stride + (size_t)h * (N + extra);
@@ -829,10 +865,26 @@ head_project_kernel(T* __restrict__ out, long long out_stride, const T* __restri
   for (int e = threadIdx.x; e < extra; e += blockDim.x) o[N + e] = xr[D + e];
   __syncthreads();
   const T* wh = w + (size_t)h * D * N;
-  for (int n = threadIdx.x; n < N; n += blockDim.x) {
+  const int groups = blockDim.x / cols, grp = threadIdx.x / cols, col = threadIdx.x - grp * cols;
+  const int per = (D + groups - 1) / groups, d0 = grp * per, d1 = min(D, d0 + per);
+  for (int n0 = 0; n0 < N; n0 += cols) {            // (several rounds only when there is one group)
+    const int n = n0 + col;
     float acc = 0.f;
-    for (int d = 0; d < D; ++d) acc += xs[d] * to_f32(wh[(size_t)d * N + n]);
-    o[n] = from_f32<T>(acc);
+    if (n < N && grp < groups) {
+#pragma unroll 8
+      for (int d = d0; d < d1; ++d) acc += xs[d] * to_f32(wh[(size_t)d * N + n]);
+    }
+    if (groups == 1) {
+      if (n < N) o[n] = from_f32<T>(acc);
+      continue;
+    }
+    if (grp < groups) red[grp * cols + col] = acc;
+    __syncthreads();
+    if (grp == 0 && n < N) {
+      float sum = red[col];
+      for (int g2 = 1; g2 < groups; ++g2) sum += red[g2 * cols + col];
+      o[n] = from_f32<T>(sum);
+    }
   }
 }
 
@@ -842,10 +894,10 @@ AF_EXPORT int af_head_project(void* out, long long out_stride, const void* x, lo
   if (n_tokens == 0) return 0;
   AF_REQUIRE(n_tokens > 0 && heads > 0 && heads < 65536 && D > 0 && N > 0 && extra >= 0 && x_pitch >= D + extra,
              "af_head_project: bad sizes");
-  AF_REQUIRE((size_t)D * sizeof(float) <= 48 * 1024, "af_head_project: %d inputs a head beyond 12288", D);
-  const int threads = N >= 256 ? 256 : ((N + 31) / 32) * 32;
+  AF_REQUIRE((size_t)(D + 256) * sizeof(float) <= 48 * 1024, "af_head_project: %d inputs a head beyond 12032", D);
+  const int cols = N >= 256 ? 256 : ((N + 31) / 32) * 32;          // outputs a round; 256 / cols groups share the inputs
   AF_DISPATCH_DTYPE(dtype, T,
-                    af_launch(head_project_kernel<T>, dim3(n_tokens, heads), dim3(threads), (size_t)D * sizeof(float),
-                              stream, (T*)out, out_stride, (const T*)x, x_stride, (const T*)w, D, N, extra, x_pitch));
+                    af_launch(head_project_kernel<T>, dim3(n_tokens, heads), dim3(256), (size_t)(D + 256) * sizeof(float),
+                              stream, (T*)out, out_stride, (const T*)x, x_stride, (const T*)w, D, N, extra, x_pitch, cols));
   AF_CHECK_LAUNCH("af_head_project");
 }

@@ -653,10 +653,9 @@ def _chunk_starts(batch, size: int):
             starts.extend(range(row, row + n, size))
             row += n
         starts.append(row)
-        host = torch.tensor(starts, dtype=torch.int32).pin_memory()
-        batch.aux[key] = (host.to(batch.tokens.device, non_blocking=True), len(starts) - 1,
-                          min(size, max(batch.seq_lens)), host)      # (the pinned rows live as long as the copy may wait)
-    return batch.aux[key][:3]
+        host = torch.tensor(starts, dtype=torch.int32)
+        batch.aux[key] = (host.to(batch.tokens.device), len(starts) - 1, min(size, max(batch.seq_lens)))
+    return batch.aux[key]
 
 
 def attn_prefill(out, q, k, v, batch, nq, nkv, hd, scale, cap, window, slopes=None, dv=None, mask: str = "window",
@@ -750,6 +749,37 @@ def attn_decode_split(out, q, kcache, vcache, page_table, slots, lens, nq, nkv, 
         _ptr(error_word(q.device), "err", torch.int32), _stream()))
 
 
+def attn_decode_latent_supported(dtype, hd: int, dv: int) -> bool:
+    """Whether :func:`attn_decode_latent` takes cached rows of ``hd`` elements with the values their first ``dv``."""
+    return dtype == torch.bfloat16 and bool(_lib().af_attn_decode_latent_supported(c_int(hd), c_int(dv)))
+
+
+def attn_decode_latent(out, q, kcache, page_table, slots, lens, nq: int, nkv: int, hd: int, dv: int, scale: float,
+                       window: int, ring_rows: int, mask: str = "window", sinks=None, gate=None, n_splits: int = 1) -> None:
+    """bfloat16 decode attention over cached rows that hold their values inside their keys (a value: the first
+    ``dv`` elements of its key row of ``hd``), on the tensor cores, the query heads of a kv head sharing every row
+    read; the visible keys cut into ``n_splits`` runs, joined by the plain kernel's merge (sinks and gate there)."""
+    B = q.shape[0]
+    if q.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("attn_decode_latent: bfloat16 only")
+    if tuple(kcache.shape[1:]) != (nkv, PAGE, hd) or not kcache.is_contiguous() or tuple(out.shape) != (B, nq * dv):
+        raise KernelError(f"attn_decode_latent: cache pages [pages, {nkv}, {PAGE}, {hd}], out [{B}, {nq * dv}]")
+    if mask not in MASKS or (sinks is not None and sinks.numel() != nq):
+        raise KernelError("attn_decode_latent: mask, or one sink a head")
+    gp, gs = _gate_args(gate, B, nq, "attn_decode_latent")
+    scratch = torch.empty(B * nq * n_splits * (dv + 2), dtype=torch.float32, device=q.device)
+    part_o, part_ml = scratch[: B * nq * n_splits * dv], scratch[B * nq * n_splits * dv:]
+    _check(_lib().af_attn_decode_latent(
+        _ptr(q), c_longlong(_rows(q, "q")), _ptr(kcache), _ptr(page_table, "page_table", torch.int32),
+        c_int(page_table.shape[1]), _ptr(slots, "slots", torch.int32), _ptr(lens, "lens", torch.int32), c_int(B), c_int(nq),
+        c_int(nkv), c_int(hd), c_int(dv), c_float(scale), c_int(window), c_int(MASKS[mask]), c_int(ring_rows),
+        c_int(n_splits), _ptr(part_o), _ptr(part_ml), _stream()))
+    _check(_lib().af_attn_decode_merge_runs(
+        _ptr(out), c_int(_rows(out, "out")), c_int(dtype_code(out.dtype)), _ptr(part_o), _ptr(part_ml),
+        _ptr(slots, "slots", torch.int32), c_int(B), c_int(nq), c_int(dv), c_int(n_splits),
+        _ptr(sinks, "sinks", torch.float32, allow_none=True), gp, gs, _stream()))
+
+
 ATTN_DECODE_MAX_SEQS = 2048     # sequences of a step that the split kernel plans for (more: the plain kernel)
 
 
@@ -789,6 +819,14 @@ def attn_decode(out, q, kv, batch, nq, nkv, hd, scale, cap, window, slopes=None,
         return
     # (a captured step sizes its cut for the longest context; the keys a token sees are bounded by its window or chunk)
     most = min(batch.max_len_after, window) if window else batch.max_len_after
+    if (kv.v is None and slopes is None and cap == 0.0 and attn_decode_latent_supported(q.dtype, hd, dv or hd)
+            and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and batch.n_seqs < 65536):
+        # wide rows with the values inside: the tensor-core kernel, runs of at least 64 keys, some two blocks an SM
+        units = batch.n_seqs * nkv * ((nq // nkv + 15) // 16)
+        n = max(1, min(-(-2 * sm_count() // units), -(-most // 64), 256))
+        attn_decode_latent(out, q, kv.k, kv.page_table, batch.slots, batch.len_after, nq, nkv, hd, dv or hd, scale,
+                           window, kv.ring_rows, mask=mask, sinks=sinks, gate=gate, n_splits=n)
+        return
     attn_decode_plain(out, q, kv.k, kv.v, kv.page_table, batch.slots, batch.len_after, nq, nkv, hd,
                       scale, cap, window, kv.ring_rows, slopes, dv=dv, mask=mask, sinks=sinks, gate=gate,
                       n_splits=plain_decode_splits(batch.n_seqs, nq, most))

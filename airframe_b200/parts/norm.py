@@ -86,7 +86,7 @@ class TanhNorm(Norm):
 
     def weight_decls(self):
         w, b, a = self.names
-        return [WeightDecl(w, (self.size,), "norm"), WeightDecl(b, (self.size,), "norm"), WeightDecl(a, (), "norm")]
+        return [WeightDecl(w, (self.size,), "gain"), WeightDecl(b, (self.size,), "norm"), WeightDecl(a, (), "gain")]
 
     def load(self, weights):
         w, b, a = self.names

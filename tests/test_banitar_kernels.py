@@ -229,6 +229,9 @@ CASES = [   # nq, nkv, dk, dv, size, mask, sink, gate, values in keys
     (4, 1, 128, 96, 130, "window", True, False, True),      # cached rows of 128 with the values inside
     (2, 2, 64, 64, 33, "window", True, False, False),
     (2, 1, 40, 40, 1, "chunk", False, False, False),        # a token sees itself alone
+    (4, 1, 320, 256, 130, "window", True, False, True),     # wide rows with the values inside: the kernel for them
+    (18, 1, 576, 512, 100, "window", True, True, True),     # (more heads than a tile of 16)
+    (6, 2, 48, 32, 5, "chunk", False, False, True),
 ]
 
 

@@ -94,11 +94,11 @@ CONFIGS = {"A": BN_A, "B": BN_B, "C": BN_C, "D": BN_D, "E": BN_E}
 
 
 def shape_weight(name, kind, t):
-    """Random values (N(0, 0.02) matrices and tables, N(0, 0.1) vectors) stretched so that every mechanism
+    """Random values (N(0, 0.02) matrices and tables, N(0, 0.1) vectors, N(1, 0.1) gains) stretched so that every mechanism
     matters: a residual stream of the order of one, projections that keep their inputs' size, so that softmaxes,
     gates and the tanh of the norms leave their middles and no sublayer drowns in another."""
     if name.endswith(".alpha"):
-        return 0.4 + t.abs() * 4.0                      # the norm's slope: 0.4 .. 1.5
+        return 0.4 + (t - 1.0).abs() * 4.0              # the norm's slope: 0.4 .. 1.5
     if name == "embed":
         return t * 50.0
     if name == "head":
@@ -110,7 +110,9 @@ def shape_weight(name, kind, t):
             return t * 15.0                             # sinks of either sign, some above the scores
         if name.endswith(".b") or name == "loop.step":
             return t * 3.0
-        return 1.0 + t * 3.0                            # norm weights around one
+        return 1.0 + t * 3.0                            # the latent's norm weight around one
+    if kind == "gain":
+        return 1.0 + (t - 1.0) * 3.0                    # norm weights around one
     return t
 
 
