@@ -888,6 +888,53 @@ head_project_kernel(T* __restrict__ out, long long out_stride, const T* __restri
   }
 }
 
+// The same for the few rows of a decode step: a block takes 32 outputs of a head for eight tokens at once, so a
+// weight is read once for all of them; its 256 threads are 8 groups that each take a stretch of the inputs
+// (short chains side by side), joined in group order through shared memory.  Grid (head, 32 outputs, 8 tokens).
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_project_few_kernel(T* __restrict__ out, long long out_stride, const T* __restrict__ x, long long x_stride,
+                        const T* __restrict__ w, int D, int N, int extra, int x_pitch, int n_tokens) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float xs[];                     // [8 tokens][D] inputs, then [8 groups][8 tokens][32] partial sums
+  float* red = xs + 8 * D;
+  const int h = blockIdx.x, n = blockIdx.y * 32 + (threadIdx.x & 31), t0 = blockIdx.z * 8;
+  const int grp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < 8 * D; i += blockDim.x) {
+    const int u = i / D, d = i - u * D;
+    xs[i] = t0 + u < n_tokens ? to_f32(x[(size_t)(t0 + u) * x_stride + (size_t)h * x_pitch + d]) : 0.f;
+  }
+  if (blockIdx.y == 0)
+    for (int i = threadIdx.x; i < 8 * extra; i += blockDim.x) {
+      const int u = i / extra, e = i - u * extra;
+      if (t0 + u < n_tokens)
+        out[(size_t)(t0 + u) * out_stride + (size_t)h * (N + extra) + N + e] = x[(size_t)(t0 + u) * x_stride + (size_t)h * x_pitch + D + e];
+    }
+  __syncthreads();
+  const int per = (D + 7) / 8, d0 = grp * per, d1 = min(D, d0 + per);
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (n < N) {
+    const T* wh = w + (size_t)h * D * N + n;
+#pragma unroll 4
+    for (int d = d0; d < d1; ++d) {
+      const float wv = to_f32(wh[(size_t)d * N]);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) acc[u] += xs[u * D + d] * wv;
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < 8; ++u) red[(grp * 8 + u) * 32 + (threadIdx.x & 31)] = acc[u];
+  __syncthreads();
+  const int u = threadIdx.x >> 5;                   // (now: the token this thread writes)
+  if (n < N && t0 + u < n_tokens) {
+    float sum = 0.f;
+#pragma unroll
+    for (int g2 = 0; g2 < 8; ++g2) sum += red[(g2 * 8 + u) * 32 + (threadIdx.x & 31)];
+    out[(size_t)(t0 + u) * out_stride + (size_t)h * (N + extra) + n] = from_f32<T>(sum);
+  }
+}
+
 AF_EXPORT int af_head_project(void* out, long long out_stride, const void* x, long long x_stride, const void* w,
                               int dtype, int n_tokens, int heads, int D, int N, int extra, int x_pitch,
                               cudaStream_t stream) {
@@ -895,6 +942,13 @@ AF_EXPORT int af_head_project(void* out, long long out_stride, const void* x, lo
   AF_REQUIRE(n_tokens > 0 && heads > 0 && heads < 65536 && D > 0 && N > 0 && extra >= 0 && x_pitch >= D + extra,
              "af_head_project: bad sizes");
   AF_REQUIRE((size_t)(D + 256) * sizeof(float) <= 48 * 1024, "af_head_project: %d inputs a head beyond 12032", D);
+  if (n_tokens <= 64 && (size_t)(8 * D + 2048) * sizeof(float) <= 48 * 1024 && (N + 31) / 32 < 65536) {
+    AF_DISPATCH_DTYPE(dtype, T,
+                      af_launch(head_project_few_kernel<T>, dim3(heads, (N + 31) / 32, (n_tokens + 7) / 8), dim3(256),
+                                (size_t)(8 * D + 2048) * sizeof(float), stream, (T*)out, out_stride, (const T*)x, x_stride,
+                                (const T*)w, D, N, extra, x_pitch, n_tokens));
+    AF_CHECK_LAUNCH("af_head_project");
+  }
   const int cols = N >= 256 ? 256 : ((N + 31) / 32) * 32;          // outputs a round; 256 / cols groups share the inputs
   AF_DISPATCH_DTYPE(dtype, T,
                     af_launch(head_project_kernel<T>, dim3(n_tokens, heads), dim3(256), (size_t)(D + 256) * sizeof(float),

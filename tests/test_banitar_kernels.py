@@ -184,6 +184,14 @@ def test_latent_rows_and_the_product_per_head(K, heads, dim, rot, rank, pitch, d
     out2 = torch.empty(T, heads * rank, dtype=dtype, device=DEV)
     K.head_project(out2, q, w, heads, dim, rank, x_pitch=P)
     close(out2.view(T, heads, -1), want[..., :rank], 1e-5 if dtype == torch.float32 else 1e-2)
+    # the few rows of a decode step go through a kernel of their own (eight tokens a block)
+    for n in (1, 5, 13):
+        few = torch.full((n, heads * (rank + rot)), float("nan"), dtype=dtype, device=DEV)
+        K.head_project(few, packed[:n].contiguous(), w, heads, dim, rank, extra=rot)
+        close(few.view(n, heads, -1), want[:n], 1e-5 if dtype == torch.float32 else 1e-2)
+        few2 = torch.empty(n, heads * rank, dtype=dtype, device=DEV)
+        K.head_project(few2, q[:n].contiguous(), w, heads, dim, rank, x_pitch=P)
+        close(few2.view(n, heads, -1), want[:n, :, :rank], 1e-5 if dtype == torch.float32 else 1e-2)
 
 
 # ---------------------------------------------------------------- attention
