@@ -3,10 +3,11 @@
 // kernel of attention_decode.cu takes.  bfloat16, tensor cores (mma.sync m16n8k16): the query heads of a kv head
 // are the 16 rows of a tile, so a row of the cache is read once for all of them.
 //
-// Grid (split, kv head x head tile, sequence); a block of four warps walks its run of the visible keys 64 at a
-// time: the tile's rows go to shared memory (zeros beyond the run), warp w takes the scores of keys 16 w .. 16 w + 15,
+// Grid (split, kv head x head tile, sequence); a block of eight warps walks its run of the visible keys 64 at a
+// time: the tile's rows go to shared memory (zeros beyond the run), warp w takes the scores of keys 8 w .. 8 w + 7
+// (two chains of products side by side, one over the even and one over the odd stretches of 32 elements),
 // the tile's maxima and sums meet in shared memory, the probabilities (bfloat16) too, and warp w then adds
-// P V into the value columns it owns (every fourth group of 16).  A block leaves its unnormalised outputs, maxima
+// P V into the value columns it owns (every eighth group of 16).  A block leaves its unnormalised outputs, maxima
 // and sums (natural exponents) where attn_decode_plain_merge_kernel of attention_plain.cu joins the runs
 // (and adds the sink and the gate).
 #include "common.cuh"
@@ -14,9 +15,9 @@
 namespace {
 
 constexpr int LA_KEYS = 64;        // keys of a tile
-constexpr int LA_WARPS = 4;
+constexpr int LA_WARPS = 8;
 constexpr int LA_MAX_DK = 640;
-constexpr int LA_CHUNKS = 10;      // groups of 16 value columns a warp owns at most (dv <= 640)
+constexpr int LA_CHUNKS = 5;       // groups of 16 value columns a warp owns at most (dv <= 640)
 
 __device__ __forceinline__ uint32_t la_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void la_ldm4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
@@ -50,8 +51,8 @@ attn_decode_latent_kernel(const __nv_bfloat16* __restrict__ q, long long q_strid
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(la_raw);            // [16][pitch]
   __nv_bfloat16* k_s = q_s + 16 * pitch;                                    // [64][pitch]
   __nv_bfloat16* p_s = k_s + LA_KEYS * pitch;                               // [16][72]
-  float* max_s = reinterpret_cast<float*>(p_s + 16 * 72);                   // [4][16]
-  float* sum_s = max_s + LA_WARPS * 16;                                     // [4][16]
+  float* max_s = reinterpret_cast<float*>(p_s + 16 * 72);                   // [warps][16]
+  float* sum_s = max_s + LA_WARPS * 16;                                     // [warps][16]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int split = blockIdx.x, b = blockIdx.z;
   const int group = nq / nkv, tiles = (group + 15) / 16;
@@ -76,7 +77,7 @@ attn_decode_latent_kernel(const __nv_bfloat16* __restrict__ q, long long q_strid
     if (r < n_heads && hi >= lo) v = *reinterpret_cast<const uint4*>(q + (size_t)b * q_stride + (size_t)(head0 + r) * dk + c * 8);
     *reinterpret_cast<uint4*>(q_s + r * pitch + c * 8) = v;
   }
-  const int n16 = dv / 16;                                      // groups of 16 value columns; warp w owns w, w + 4, ...
+  const int n16 = dv / 16;                                      // groups of 16 value columns; warp w owns w, w + 8, ...
   float o[LA_CHUNKS][2][4];
 #pragma unroll
   for (int c = 0; c < LA_CHUNKS; ++c)
@@ -88,7 +89,7 @@ attn_decode_latent_kernel(const __nv_bfloat16* __restrict__ q, long long q_strid
   const int* pt = page_table + (size_t)max(slot, 0) * max_pages;
   for (int j0 = lo; j0 <= hi; j0 += LA_KEYS) {
     __syncthreads();                                            // the tile before is done with (and q_s is written)
-    // ---- 64 rows of the cache, zeros beyond the run: a warp takes every fourth row, all copies in flight at once
+    // ---- 64 rows of the cache, zeros beyond the run: a warp takes every eighth row, all copies in flight at once
     for (int r = warp; r < LA_KEYS; r += LA_WARPS) {
       const int j = j0 + r;
       const __nv_bfloat16* src = kcache;
@@ -103,24 +104,26 @@ attn_decode_latent_kernel(const __nv_bfloat16* __restrict__ q, long long q_strid
     asm volatile("cp.async.commit_group;" ::: "memory");
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
-    // ---- scores of this warp's 16 keys: two tiles of 8
-    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-    for (int kk = 0; kk < dk; kk += 16) {
+    // ---- scores of this warp's 8 keys: one load brings a key tile's operands of 32 elements, two products
+    float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int kk = 0; kk < dk; kk += 32) {
       uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+      la_ldm4(la_smem(k_s + (warp * 8 + (lane & 7)) * pitch + kk + (lane >> 3) * 8), b0, b1, b2, b3);
       la_ldm4(la_smem(q_s + (lane & 15) * pitch + kk + (lane >> 4) * 8), a0, a1, a2, a3);
-      la_ldm4(la_smem(k_s + (warp * 16 + (lane >> 4) * 8 + (lane & 7)) * pitch + kk + ((lane >> 3) & 1) * 8), b0, b1, b2, b3);
-      la_mma(s[0], a0, a1, a2, a3, b0, b1);
-      la_mma(s[1], a0, a1, a2, a3, b2, b3);
+      la_mma(sa, a0, a1, a2, a3, b0, b1);
+      if (kk + 16 < dk) {                                       // (dk is a multiple of 16: the last stretch may be half)
+        la_ldm4(la_smem(q_s + (lane & 15) * pitch + kk + 16 + (lane >> 4) * 8), a0, a1, a2, a3);
+        la_mma(sb, a0, a1, a2, a3, b2, b3);
+      }
     }
+    float s[4];
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-    for (int n = 0; n < 2; ++n)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int j = j0 + warp * 16 + n * 8 + 2 * t + (e & 1);
-        s[n][e] = j <= hi ? s[n][e] * scale : -INFINITY;
-        mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
-      }
+    for (int e = 0; e < 4; ++e) {
+      const int j = j0 + warp * 8 + 2 * t + (e & 1);
+      s[e] = j <= hi ? (sa[e] + sb[e]) * scale : -INFINITY;
+      mx[e >> 1] = fmaxf(mx[e >> 1], s[e]);
+    }
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
@@ -128,26 +131,27 @@ attn_decode_latent_kernel(const __nv_bfloat16* __restrict__ q, long long q_strid
       if (t == 0) max_s[warp * 16 + g + 8 * r] = mx[r];
     }
     __syncthreads();
-    float corr[2], ref[2], sm[2] = {0.f, 0.f};
+    float corr[2], ref[2], sm[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       const int row = g + 8 * r;
-      const float tile_max = fmaxf(fmaxf(max_s[row], max_s[16 + row]), fmaxf(max_s[32 + row], max_s[48 + row]));
+      float tile_max = max_s[row];
+#pragma unroll
+      for (int w2 = 1; w2 < LA_WARPS; ++w2) tile_max = fmaxf(tile_max, max_s[w2 * 16 + row]);
       const float m_new = fmaxf(m_run[r], tile_max);
       ref[r] = m_new == -INFINITY ? 0.f : m_new;
       corr[r] = m_run[r] == -INFINITY ? 0.f : __expf(m_run[r] - ref[r]);
       m_run[r] = m_new;
     }
-#pragma unroll
-    for (int n = 0; n < 2; ++n) {
-      const float p0 = __expf(s[n][0] - ref[0]), p1 = __expf(s[n][1] - ref[0]);
-      const float p2 = __expf(s[n][2] - ref[1]), p3 = __expf(s[n][3] - ref[1]);
+    {
+      const float p0 = __expf(s[0] - ref[0]), p1 = __expf(s[1] - ref[0]);
+      const float p2 = __expf(s[2] - ref[1]), p3 = __expf(s[3] - ref[1]);
       const __nv_bfloat162 lo2 = __floats2bfloat162_rn(p0, p1), hi2 = __floats2bfloat162_rn(p2, p3);
       // (the sums take the rounded values that the product will see)
-      sm[0] += __low2float(lo2) + __high2float(lo2);
-      sm[1] += __low2float(hi2) + __high2float(hi2);
-      *reinterpret_cast<__nv_bfloat162*>(p_s + g * 72 + warp * 16 + n * 8 + 2 * t) = lo2;
-      *reinterpret_cast<__nv_bfloat162*>(p_s + (g + 8) * 72 + warp * 16 + n * 8 + 2 * t) = hi2;
+      sm[0] = __low2float(lo2) + __high2float(lo2);
+      sm[1] = __low2float(hi2) + __high2float(hi2);
+      *reinterpret_cast<__nv_bfloat162*>(p_s + g * 72 + warp * 8 + 2 * t) = lo2;
+      *reinterpret_cast<__nv_bfloat162*>(p_s + (g + 8) * 72 + warp * 8 + 2 * t) = hi2;
     }
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
@@ -159,7 +163,10 @@ attn_decode_latent_kernel(const __nv_bfloat16* __restrict__ q, long long q_strid
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       const int row = g + 8 * r;
-      l_run[r] = l_run[r] * corr[r] + ((sum_s[row] + sum_s[16 + row]) + (sum_s[32 + row] + sum_s[48 + row]));
+      float tile_sum = 0.f;
+#pragma unroll
+      for (int w2 = 0; w2 < LA_WARPS; ++w2) tile_sum += sum_s[w2 * 16 + row];
+      l_run[r] = l_run[r] * corr[r] + tile_sum;
     }
     // ---- O += P V over the value columns this warp owns
 #pragma unroll
