@@ -491,8 +491,8 @@ def _banitar_sizes(width, layers, heads, kv_heads, attn_dim, lat_dim, rot_dim, v
     run twice, and the Gemma-2 model of the same width, feed-forward and vocabulary with as many layers as that
     makes runs."""
     attn = {"heads": heads, "kv_heads": kv_heads, "dim": attn_dim, "vdim": attn_dim, "mask": {"size": window},
-            "scale": attn_dim ** -0.5, "rot": {"base": 1e6, "dims": attn_dim,
-                                              "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+            "scale": attn_dim ** -0.5, "rot": {"base": 10000.0, "dims": attn_dim,
+                                              "scaling": {"factor": 4.0, "original": 4096, "fast": 16.0, "slow": 2.0}}}
     latent = {"heads": heads, "dim": lat_dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank,
               "mask": {"size": window}, "scale": (lat_dim + rot_dim) ** -0.5, "rot": {"base": 1e4, "dims": rot_dim}}
     bn = {"architecture": "Banitar", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
