@@ -96,18 +96,25 @@ AF_EXPORT int af_add_tanh_norm(float* x, const void* a, int a_dtype, int n_parts
 }
 
 // out[r] = [a[r] | b[r]] in the compute dtype: the input rows of a product over two float streams.
-template <typename T>
+// V elements a thread (4 where both widths divide by 4: a group then lies in one of the two streams).
+template <typename T, int V>
 __global__ void __launch_bounds__(256)
 concat_cast_kernel(T* __restrict__ out, const float* __restrict__ a, const float* __restrict__ b, int ha, int hb,
                    size_t total) {
   pdl_launch_dependents();
   pdl_wait();
-  const size_t at = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t at = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * V;
   if (at >= total) return;
   const int wdt = ha + hb;
   const size_t r = at / wdt;
   const int i = (int)(at - r * wdt);
-  out[at] = from_f32<T>(i < ha ? a[r * ha + i] : b[r * hb + (i - ha)]);
+  const float* src = i < ha ? a + r * ha + i : b + r * hb + (i - ha);
+  if (V == 4) {
+    const float4 v = *reinterpret_cast<const float4*>(src);
+    out[at] = from_f32<T>(v.x), out[at + 1] = from_f32<T>(v.y), out[at + 2] = from_f32<T>(v.z), out[at + 3] = from_f32<T>(v.w);
+  } else {
+    out[at] = from_f32<T>(*src);
+  }
 }
 
 AF_EXPORT int af_concat_cast(void* out, int dtype, const float* a, const float* b, int n_rows, int ha, int hb,
@@ -115,11 +122,18 @@ AF_EXPORT int af_concat_cast(void* out, int dtype, const float* a, const float* 
   if (n_rows == 0) return 0;
   AF_REQUIRE(n_rows > 0 && ha > 0 && hb > 0, "af_concat_cast: bad sizes");
   const size_t total = (size_t)n_rows * (ha + hb);
-  const size_t blocks = (total + 255) / 256;
+  const bool vec = ha % 4 == 0 && hb % 4 == 0 && (((uintptr_t)a | (uintptr_t)b) & 15) == 0;
+  const size_t blocks = ((vec ? total / 4 : total) + 255) / 256;
   AF_REQUIRE(blocks < (1ull << 31), "af_concat_cast: too many rows");
-  AF_DISPATCH_DTYPE(dtype, T,
-                    af_launch(concat_cast_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, (T*)out, a, b, ha, hb,
-                              total));
+  if (vec) {
+    AF_DISPATCH_DTYPE(dtype, T,
+                      af_launch(concat_cast_kernel<T, 4>, dim3((unsigned)blocks), dim3(256), 0, stream, (T*)out, a, b, ha, hb,
+                                total));
+  } else {
+    AF_DISPATCH_DTYPE(dtype, T,
+                      af_launch(concat_cast_kernel<T, 1>, dim3((unsigned)blocks), dim3(256), 0, stream, (T*)out, a, b, ha, hb,
+                                total));
+  }
   AF_CHECK_LAUNCH("af_concat_cast");
 }
 

@@ -182,7 +182,7 @@ def load(c, dtype, max_tokens=64 * 24, **kw):
 
 
 @gpu
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 def test_whole_prompt_and_token_by_token(name, dtype, tmp_path_factory):
     """A prompt in one step; the same tokens with the last 40 one by one (the captured decode step);
     and a prompt of one token followed by single tokens only (the first tokens of a sequence, decoded)."""
@@ -202,7 +202,7 @@ def test_whole_prompt_and_token_by_token(name, dtype, tmp_path_factory):
 
 
 @gpu
-@pytest.mark.parametrize("name", ["A", "B", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "D", "F"])
 def test_unequal_batches_and_slots_used_again(name, dtype, tmp_path_factory):
     """Requests of unequal lengths (one of a single token, one longer than its windows) in batches, then
     decoded together, the shorter ones leaving; twice, so that slots and pages are used again."""
@@ -323,7 +323,7 @@ def test_layers_agree_one_by_one(tmp_path_factory):
             if run >= 0:
                 self.x.append(x.detach().cpu().double())
 
-    for name in ("A", "B", "C", "D", "E"):
+    for name in ("A", "B", "C", "D", "E", "F"):
         c = case(name, tmp_path_factory)
         rt = load(c, "float32")
         ids = replay.random_ids(c["cfg"]["vocab"], 75, 2)

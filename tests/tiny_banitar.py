@@ -90,7 +90,21 @@ BN_E = {
     "loop": {"start": 2, "stop": 3, "times": 4},
 }
 
-CONFIGS = {"A": BN_A, "B": BN_B, "C": BN_C, "D": BN_D, "E": BN_E}
+# more query heads on a kv head than a tile of 16 rows holds; a chunk and a window shorter than a cache page on the
+# tensor-core kernels; cached rows of 64 and of 160 (the kernel for wide rows); a stretch of three layers run twice
+BN_F = {
+    "architecture": "Banitar", "vocab": 150, "width": 192, "embedding": {"scale": 1.2}, "norm": {"eps": 1e-6},
+    "layers": [
+        _layer("attention", _attn(20, 1, 64, 64, 20, 64, 1000.0, 0.15), ff=128),
+        _layer("latent_attention", _latent(20, 16, 16, 32, 48, 9, 1000.0, 0.2)),
+        _layer("attention", _attn(12, 4, 128, 128, 45, 96, 1e5, 0.1, {"factor": 16.0, "original": 32, "fast": 8.0,
+                                                                     "slow": 1.0}), ff=96),
+        _layer("latent_attention", _latent(18, 32, 32, 64, 128, 50, 1e4, 0.15), ff=64),
+    ],
+    "loop": {"start": 0, "stop": 3, "times": 2},
+}
+
+CONFIGS = {"A": BN_A, "B": BN_B, "C": BN_C, "D": BN_D, "E": BN_E, "F": BN_F}
 
 
 def shape_weight(name, kind, t):
