@@ -80,8 +80,9 @@ def test_tanh_norm_alone_and_fused(K, H, out_dtype):
         assert torch.equal(x1, x2)
 
 
-def test_reentry_sums(K):
-    T, H = 19, 50
+@pytest.mark.parametrize("H", [50, 72])
+def test_reentry_sums(K, H):
+    T = 19
     x, x0 = torch.randn(T, H, device=DEV), torch.randn(T, H, device=DEV)
     for dt in (torch.float32, torch.bfloat16):
         both = torch.empty(T, 2 * H, dtype=dt, device=DEV)
