@@ -296,7 +296,7 @@ def test_attention_of_prompts_and_single_tokens(K, nq, nkv, dk, dv, size, mask, 
         close(o.view(1, nq, dv), want[L - 1: L], tol)
 
 
-@pytest.mark.parametrize("mask,size", [("window", 75), ("chunk", 75), ("window", 130), ("chunk", 64)])
+@pytest.mark.parametrize("mask,size", [("window", 75), ("chunk", 75), ("window", 130), ("chunk", 64), ("window", 190), ("chunk", 128)])
 @pytest.mark.parametrize("dk", [40, 128])
 def test_a_key_at_the_edge_shows(K, mask, size, dk):
     """One key's score stands far above all others.  Placed at the first position that the last token still sees,
