@@ -622,7 +622,9 @@ AF_EXPORT int af_head_gate(void* x, long long x_stride, int dtype, const float* 
 //   with `norm_after`: r / sqrt(mean(r^2) + eps) over the whole head (no weight)
 // and written to the packed row [q | k | v] of the compute dtype; a k head also goes to its row of the
 // cache, and its value head (the raw x with `v_from_k`, else the projection's own v head plus its bias) to
-// the packed row and the cache.
+// the packed row and the cache.  `pitch` > 0 (>= hd and >= dv): the heads of the packed row and the rows of the
+// cache are that many elements apart, zeros behind a head's own (a mixer pads its heads up to a size that the
+// tensor-core attention kernels take); 0: q and k heads hd apart, v heads dv apart.
 template <typename T>
 __global__ void __launch_bounds__(128)
 qk_norm_rope_store_kernel(T* __restrict__ qkv, long long out_stride, const float* __restrict__ proj, long long ld,
@@ -632,7 +634,7 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, long long out_stride, const float
                           const int* __restrict__ slots, const int* __restrict__ len_after,
                           const float* __restrict__ inv_freq, int n_tokens, int nq, int nkv, int hd, int dv, int rot_dim,
                           int pairing, T* __restrict__ kcache, T* __restrict__ vcache,
-                          const int* __restrict__ page_table, int max_pages, int ring_rows) {
+                          const int* __restrict__ page_table, int max_pages, int ring_rows, int pitch) {
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31;
   const long long wi = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -640,6 +642,7 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, long long out_stride, const float
   const int t = (int)(wi / (nq + nkv)), head = (int)(wi % (nq + nkv));
   const bool is_k = head >= nq;
   const int pos = positions[t];
+  const int pk = pitch > 0 ? pitch : hd, pv = pitch > 0 ? pitch : dv;      // elements between heads (and of a cache row)
   // where a k head's row goes in the cache
   T *kdst = nullptr, *vdst = nullptr;
   if (kcache != nullptr && is_k) {
@@ -651,8 +654,8 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, long long out_stride, const float
         const int page = page_table[(size_t)slot * max_pages + r / AF_PAGE];
         if (AF_INDEX_OK(page >= 0, page)) {
           const size_t at = ((size_t)page * nkv + (head - nq)) * AF_PAGE + r % AF_PAGE;
-          kdst = kcache + at * hd;
-          vdst = vcache + at * dv;
+          kdst = kcache + at * pk;
+          vdst = vcache + at * pv;
         }
       }
     }
@@ -662,7 +665,7 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, long long out_stride, const float
   const float* xb = bias ? bias + (size_t)head * hd : nullptr;
   const float* w = is_k ? k_weight : q_weight;
   T* orow = qkv + (size_t)t * out_stride;
-  T* dst = orow + (size_t)head * hd;                        // q heads and k heads keep their places
+  T* dst = orow + (size_t)head * pk;                        // q heads and k heads keep their places
   float inv = 1.f;
   if (w != nullptr) {
     float ss = 0.f;
@@ -707,14 +710,18 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, long long out_stride, const float
     dst[i] = v;
     if (kdst != nullptr) kdst[i] = v;
   }
+  for (int i = hd + lane; i < pk; i += 32) {                // the padding behind the head
+    dst[i] = from_f32<T>(0.f);
+    if (kdst != nullptr) kdst[i] = from_f32<T>(0.f);
+  }
   if (is_k) {
     const int g = head - nq;
-    const size_t v_off = (size_t)(nq + nkv) * hd + (size_t)g * dv;          // the value head's place, in both rows
+    const size_t v_off = (size_t)(nq + nkv) * hd + (size_t)g * dv;          // the value head's place in the projection
     const float* vx = v_from_k ? x : proj + (size_t)t * ld + v_off;
     const float* vb = bias == nullptr ? nullptr : (v_from_k ? xb : bias + v_off);
-    T* vrow = orow + v_off;
-    for (int i = lane; i < dv; i += 32) {
-      const T v = from_f32<T>(vx[i] + (vb && !v_from_k ? vb[i] : 0.f));
+    T* vrow = orow + (size_t)(nq + nkv) * pk + (size_t)g * pv;              // and in the packed row
+    for (int i = lane; i < pv; i += 32) {
+      const T v = from_f32<T>(i < dv ? vx[i] + (vb && !v_from_k ? vb[i] : 0.f) : 0.f);
       vrow[i] = v;
       if (vdst != nullptr) vdst[i] = v;
     }
@@ -727,9 +734,11 @@ AF_EXPORT int af_qk_norm_rope_store(void* qkv, int dtype, long long out_stride, 
                                     const int* positions, const int* seq_of_token, const int* slots,
                                     const int* len_after, const float* inv_freq, int n_tokens, int nq, int nkv, int hd,
                                     int dv, int rot_dim, int pairing, void* kcache, void* vcache, const int* page_table,
-                                    int max_pages, int ring_rows, cudaStream_t stream) {
+                                    int max_pages, int ring_rows, int pitch, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   AF_REQUIRE(n_tokens > 0 && nq > 0 && nkv > 0 && hd > 0 && dv > 0, "af_qk_norm_rope_store: bad sizes");
+  AF_REQUIRE(pitch == 0 || (pitch >= hd && pitch >= dv), "af_qk_norm_rope_store: pitch %d below the heads' sizes", pitch);
+
   AF_REQUIRE(!v_from_k || dv == hd, "af_qk_norm_rope_store: values that are the keys have their size");
   AF_REQUIRE(rot_dim >= 0 && rot_dim <= hd && rot_dim % 2 == 0,
              "af_qk_norm_rope_store: rotary dim %d must be even and <= head_dim %d", rot_dim, hd);
@@ -744,7 +753,7 @@ AF_EXPORT int af_qk_norm_rope_store(void* qkv, int dtype, long long out_stride, 
                     af_launch(qk_norm_rope_store_kernel<T>, dim3((unsigned)blocks), dim3(128), 0, stream, (T*)qkv,
                               out_stride, proj, ld, bias, q_weight, k_weight, eps, norm_after, magnitude, v_from_k,
                               positions, seq_of_token, slots, len_after, inv_freq, n_tokens, nq, nkv, hd, dv, rot_dim,
-                              pairing, (T*)kcache, (T*)vcache, page_table, max_pages, ring_rows));
+                              pairing, (T*)kcache, (T*)vcache, page_table, max_pages, ring_rows, pitch));
   AF_CHECK_LAUNCH("af_qk_norm_rope_store");
 }
 

@@ -19,6 +19,7 @@ F32, BF16 = 0, 1
 ACTIVATIONS = {"gelu_tanh": 0, "silu": 1}
 PAIRINGS = {"half": 0, "adjacent": 1}
 MASKS = {"window": 0, "chunk": 1}      # the last `size` positions / the position's own chunk of `size`
+FAST_HEAD_SIZES = (64, 128, 256)       # head sizes that the bfloat16 tensor-core attention kernels take between them
 
 
 class KernelError(RuntimeError):
@@ -937,7 +938,7 @@ def gated_scan(y, proj, off_z: int, off_x: int, off_g: int, bz, bx, state, batch
 
 def qk_norm_rope_store(qkv, proj, batch, nq: int, nkv: int, hd: int, inv_freq, rot_dim: int, pairing: str,
                        q_weight=None, k_weight=None, eps: float = 0.0, v_from_k: bool = False, kv=None,
-                       bias=None, norm_after: bool = False, magnitude: float = 1.0, dv=None) -> None:
+                       bias=None, norm_after: bool = False, magnitude: float = 1.0, dv=None, pitch: int = 0) -> None:
     """From float32 projection rows [q heads | k heads (| v heads of ``dv`` values)], plus ``bias`` (float32,
     laid out like a row) when given: q and k heads normalised per head
     (x * rsqrt(mean x^2 + eps) * weight, the weight of ``hd`` values shared by the heads; no weights: as
@@ -945,12 +946,17 @@ def qk_norm_rope_store(qkv, proj, batch, nq: int, nkv: int, hd: int, inv_freq, r
     ``norm_after`` divided by their root mean square over the head after that (eps inside the root, no weight),
     into the packed rows ``qkv`` [q | k | v] of the
     compute dtype; the value heads are the raw k heads of the projection (``v_from_k``) or the projection's own.
-    With ``kv`` (the layer's view of its cache pages) k and v also go to each token's row of its page."""
+    With ``kv`` (the layer's view of its cache pages) k and v also go to each token's row of its page.
+    ``pitch`` > 0: every head of ``qkv`` and every row of the cache holds that many elements (at least ``hd`` and
+    ``dv``), zeros behind its own."""
     T = proj.shape[0]
     dv = dv or hd
+    pk, pv = (pitch, pitch) if pitch else (hd, dv)
+    if pitch and (pitch < hd or pitch < dv):
+        raise KernelError(f"qk_norm_rope_store: a pitch of {pitch} below the heads' {hd} and {dv}")
     width_in = (nq + nkv) * hd if v_from_k else (nq + nkv) * hd + nkv * dv
-    if proj.shape[1] < width_in or tuple(qkv.shape) != (T, (nq + nkv) * hd + nkv * dv):
-        raise KernelError(f"qk_norm_rope_store: projection of {width_in} columns into rows of {(nq + nkv) * hd + nkv * dv}")
+    if proj.shape[1] < width_in or tuple(qkv.shape) != (T, (nq + nkv) * pk + nkv * pv):
+        raise KernelError(f"qk_norm_rope_store: projection of {width_in} columns into rows of {(nq + nkv) * pk + nkv * pv}")
     if pairing not in PAIRINGS or inv_freq.numel() != rot_dim // 2:
         raise KernelError("qk_norm_rope_store: pairing, or inv_freq does not hold rot_dim / 2 values")
     for wgt in (q_weight, k_weight):
@@ -962,9 +968,9 @@ def qk_norm_rope_store(qkv, proj, batch, nq: int, nkv: int, hd: int, inv_freq, r
     max_pages = ring = 0
     if kv is not None:
         kc, vc, pt, ring = kv.k, kv.v, kv.page_table, kv.ring_rows
-        if kc.dtype != qkv.dtype or tuple(kc.shape[1:]) != (nkv, PAGE, hd) or vc is None \
-                or tuple(vc.shape[1:]) != (nkv, PAGE, dv) or not kc.is_contiguous() or not vc.is_contiguous():
-            raise KernelError(f"qk_norm_rope_store: cache pages must be [pages, {nkv}, {PAGE}, {hd}] (values {dv}) "
+        if kc.dtype != qkv.dtype or tuple(kc.shape[1:]) != (nkv, PAGE, pk) or vc is None \
+                or tuple(vc.shape[1:]) != (nkv, PAGE, pv) or not kc.is_contiguous() or not vc.is_contiguous():
+            raise KernelError(f"qk_norm_rope_store: cache pages must be [pages, {nkv}, {PAGE}, {pk}] (values {pv}) "
                               "of the rows' dtype")
         max_pages = pt.shape[1]
     pp, ld = _f32_rows(proj, "proj")
@@ -978,7 +984,7 @@ def qk_norm_rope_store(qkv, proj, batch, nq: int, nkv: int, hd: int, inv_freq, r
         _ptr(batch.slots, "slots", torch.int32), _ptr(batch.len_after, "len_after", torch.int32),
         _ptr(inv_freq, "inv_freq", torch.float32), c_int(T), c_int(nq), c_int(nkv), c_int(hd), c_int(dv), c_int(rot_dim),
         c_int(PAIRINGS[pairing]), _ptr(kc, allow_none=True), _ptr(vc, allow_none=True),
-        _ptr(pt, "page_table", torch.int32, allow_none=True), c_int(max_pages), c_int(ring), _stream()))
+        _ptr(pt, "page_table", torch.int32, allow_none=True), c_int(max_pages), c_int(ring), c_int(pitch), _stream()))
 
 
 def attn_prefill_fast_head(size: int) -> int:

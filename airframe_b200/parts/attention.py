@@ -105,6 +105,15 @@ class Attention(Mixer):
                 and type(self.position).encode is not PositionEncoding.encode:
             raise ConfigError(f"attention: qk_norm and shared values go with a rotary encoding or none, "
                               f"not with '{self.position.kind}'")
+        # bfloat16 heads of a size the tensor-core attention kernels do not take are padded with zeros up to one they
+        # do (96 -> 128), in the packed rows and in the cache, where that costs at most twice the elements: the
+        # packing kernel writes the padding, the output projection's weight gets zero columns for it
+        self.pad = 0
+        big = max(self.hd, self.dv)
+        if ctx.compute_dtype == torch.bfloat16 and self.packs and not self.v_from_k:
+            fit = next((p for p in kernels.FAST_HEAD_SIZES if p >= big), 0)
+            if fit and fit <= 2 * big and (fit != self.hd or fit != self.dv):
+                self.pad = fit
         self.q_norm_w = self.k_norm_w = self.bias = self.sinks = None
         self.w_qkv = None
         self.w_o = None
@@ -112,6 +121,8 @@ class Attention(Mixer):
 
     def kv_need(self):
         # (a chunk's keys all lie within the last ``window`` positions: the ring of a window serves it)
+        if self.pad:
+            return KVNeed(self.nkv, self.pad, self.window)
         return KVNeed(self.nkv, self.hd, self.window, None if self.dv == self.hd else self.dv)
 
     def weight_decls(self):
@@ -146,6 +157,10 @@ class Attention(Mixer):
         if self.sink_name:
             self.sinks = weights[self.sink_name].to(torch.float32).contiguous()
         self.w_o = weights[o].to(dt).contiguous()
+        if self.pad:
+            wide = torch.zeros(self.hidden, self.nq, self.pad, dtype=dt, device=self.w_o.device)
+            wide[:, :, : self.dv] = self.w_o.view(self.hidden, self.nq, self.dv)
+            self.w_o = wide.view(self.hidden, self.nq * self.pad).contiguous()
         self.position.load(weights)
         if self.qk_norm is not None and not self.norm_after:
             self.q_norm_w = weights[self.qk_norm["q_weight"]].to(torch.float32).contiguous()
@@ -166,8 +181,8 @@ class Attention(Mixer):
         return 4 if self.ctx.compute_dtype == torch.float32 else 2
 
     def decode_bytes(self, lens) -> int:
-        weights = (self.w_qkv.shape[0] * self.hidden + self.hidden * self.nq * self.dv) * self._el()
-        kv_row = self.nkv * (self.hd + self.dv) * self._el()
+        weights = (self.w_qkv.numel() + self.w_o.numel()) * self._el()
+        kv_row = self.nkv * (2 * self.pad if self.pad else self.hd + self.dv) * self._el()
         return weights + sum(kv_row * self._visible(n - 1) for n in lens)
 
     def _visible(self, pos: int) -> int:
@@ -217,7 +232,8 @@ class Attention(Mixer):
         (from the raw key projection, or their own heads), all packed and the cache written: one kernel."""
         nq, nkv, hd = self.nq, self.nkv, self.hd
         proj = linear(x, self.w_qkv, out_dtype=torch.float32)
-        qkv = torch.empty(x.shape[0], (nq + nkv) * hd + nkv * self.dv, dtype=x.dtype, device=x.device)
+        width = (nq + 2 * nkv) * self.pad if self.pad else (nq + nkv) * hd + nkv * self.dv
+        qkv = torch.empty(x.shape[0], width, dtype=x.dtype, device=x.device)
         rope = self.position if isinstance(self.position, Rope) else None
         if rope is not None and rope.rotary_dim > hd:
             raise ConfigError(f"rope: rotary_dim {rope.rotary_dim} exceeds head_dim {hd}")
@@ -228,7 +244,8 @@ class Attention(Mixer):
             q_weight=self.q_norm_w, k_weight=self.k_norm_w,
             eps=float(self.qk_norm["eps"]) if self.qk_norm is not None else 0.0,
             v_from_k=self.v_from_k, kv=view.kv if view.writes else None, bias=self.bias,
-            norm_after=self.norm_after, magnitude=rope.magnitude if rope is not None else 1.0, dv=self.dv)
+            norm_after=self.norm_after, magnitude=rope.magnitude if rope is not None else 1.0, dv=self.dv,
+            pitch=self.pad)
         gate = None
         if self.gate_name:
             at = (nq + nkv) * hd + (0 if self.v_from_k else nkv * self.dv)
@@ -257,12 +274,15 @@ class Attention(Mixer):
                 self.position.encode(qkv, batch, nq, nkv, hd, parts=parts)
                 kernels.store_kv(qkv, batch, nq, nkv, hd, kv)
         slopes = self.position.score_slopes(nq)
+        dv = self.dv
+        if self.pad:                 # (from here on the heads are what the packing kernel made of them)
+            hd = dv = self.pad
         q = qkv[:, : nq * hd]
         k = qkv[:, nq * hd: (nq + nkv) * hd]
         v = qkv[:, (nq + nkv) * hd:]
-        ctx = torch.empty(x.shape[0], nq * self.dv, dtype=x.dtype, device=x.device)
+        ctx = torch.empty(x.shape[0], nq * dv, dtype=x.dtype, device=x.device)
         window = self.window or 0
-        more = {"dv": self.dv, "mask": self.mask, "sinks": self.sinks, "gate": gate}
+        more = {"dv": dv, "mask": self.mask, "sinks": self.sinks, "gate": gate}
         if batch.is_prefill:
             if not view.writes:
                 k, v = batch.step_kv[view.cache_id]

@@ -97,8 +97,8 @@ BN_F = {
     "layers": [
         _layer("attention", _attn(20, 1, 64, 64, 20, 64, 1000.0, 0.15), ff=128),
         _layer("latent_attention", _latent(20, 16, 16, 32, 48, 9, 1000.0, 0.2)),
-        _layer("attention", _attn(12, 4, 128, 128, 45, 96, 1e5, 0.1, {"factor": 16.0, "original": 32, "fast": 8.0,
-                                                                     "slow": 1.0}), ff=96),
+        _layer("attention", _attn(12, 4, 96, 80, 45, 64, 1e5, 0.1, {"factor": 16.0, "original": 32, "fast": 8.0,
+                                                                   "slow": 1.0}), ff=96),     # (heads padded to 128)
         _layer("latent_attention", _latent(18, 32, 32, 64, 128, 50, 1e4, 0.15), ff=64),
     ],
     "loop": {"start": 0, "stop": 3, "times": 2},
